@@ -7,6 +7,7 @@ from .registry import (load_config, read_config_json, register_architecture,
 from .gemma3 import Gemma3Config
 from .ramilorn import RamilornConfig
 from .zazerax import ZazeraxConfig
+from .bovozen import BovozenConfig
 
 __all__ = [
     "AttentionSpec", "BlockSpec", "ConfigError", "GatedFeedForwardSpec", "LayerCall",
@@ -15,4 +16,5 @@ __all__ = [
     "read_config_json", "register_architecture", "registered_architectures",
     "resolve_architecture", "Gemma3Config", "ZazeraxConfig", "DenseFeedForwardSpec",
     "DistanceBiasSpec", "IdentityNormSpec", "LatentAttentionSpec", "WavelengthScalingSpec",
+    "BovozenConfig",
 ]

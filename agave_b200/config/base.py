@@ -89,6 +89,26 @@ class DistanceBiasSpec:
 
 
 @dataclass(frozen=True)
+class DistanceSlopeSpec:
+    """A bias that falls linearly with distance: slope_a * (t - j) is taken off the scaled
+    score of head a, slope_a = 2 ** (-exponent * (a + 1) / n_heads) for a = 0 .. n_heads - 1.
+    ``reach``: the greatest distance a query can see plus one (the model's positions, or the
+    mask's size where that is less); it sizes the table the kernels index by distance."""
+    exponent: float = 8.0
+    reach: int = 0
+
+
+@dataclass(frozen=True)
+class ValueMixSpec:
+    """Values that lean towards an earlier layer's: v <- (1 - m) v + m v_first, m a learned
+    scalar (tensor ``value_mix``), v_first the values the call named ``source`` (a cache entry
+    of the run order) made for the same token before its own mixing.  ``source`` None: this
+    layer is the source; it mixes nothing and keeps its values for the others (its own
+    ``value_mix`` tensor exists and is unused)."""
+    source: Optional[int] = None
+
+
+@dataclass(frozen=True)
 class QueryTemperatureSpec:
     """The queries at position p are multiplied by 1 + coef * ln(floor((p + 1) / every) + 1):
     attention sharpens in steps as the context grows."""
@@ -128,6 +148,11 @@ class AttentionSpec:
     # the softmax denominator)
     fixed_sink: Optional[float] = None
     distance_bias: Optional[DistanceBiasSpec] = None
+    # position p sees j <= p only inside its own block of this many positions, counted from
+    # position 0 of the sequence (floor(p / chunk) == floor(j / chunk)); not with ``window``
+    chunk: Optional[int] = None
+    distance_slope: Optional[DistanceSlopeSpec] = None
+    value_mix: Optional[ValueMixSpec] = None
 
     @property
     def v_dim(self) -> int:
@@ -157,6 +182,31 @@ class LatentAttentionSpec:
 
 
 @dataclass(frozen=True)
+class ChannelDeltaSpec:
+    """A recurrent mixer: the gated delta rule with a decay per key channel.
+
+    q, k (``n_qk_heads`` heads of ``head_dim``) and v (``n_heads`` heads of ``value_dim``)
+    pass a causal convolution over ``conv_taps`` tokens per channel and silu; q and k heads
+    become unit vectors (x / sqrt(sum x^2 + unit_eps)), q times head_dim ** -0.5.  Per head,
+    with beta = sigmoid(W_b x) and the decay g = exp(-exp(A_log) * softplus(W_a2 W_a1 x +
+    dt_bias)) per key channel:  S <- diag(g) S; u = beta (v - S^T k); S <- S + k u^T;
+    o = S^T q.  o / rms(o) (``eps``) * weight * sigmoid(W_g2 W_g1 x) feeds the output
+    product.  ``decay_rank`` and ``gate_rank`` are the widths of the two bottlenecks.  The
+    state (S in 32-bit and the convolution's last conv_taps - 1 inputs) is a fixed size per
+    sequence."""
+    kind: str = "channel_delta"
+    n_heads: int = 0
+    n_qk_heads: int = 0
+    head_dim: int = 0
+    value_dim: int = 0
+    conv_taps: int = 1
+    decay_rank: int = 0
+    gate_rank: int = 0
+    eps: float = 1e-6
+    unit_eps: float = 1e-6
+
+
+@dataclass(frozen=True)
 class GatedFeedForwardSpec:
     """down(act(gate x) * up x), dense (src/models/gemma3.zig:840-872)."""
     kind: str = "gated_dense"
@@ -166,7 +216,8 @@ class GatedFeedForwardSpec:
 
 @dataclass(frozen=True)
 class DenseFeedForwardSpec:
-    """down(act(up x)), dense, no gate; "relu2" is max(z, 0)^2."""
+    """down(act(up x)), dense, no gate; "relu2" is max(z, 0)^2, "gelu_erf" is
+    z / 2 * (1 + erf(z / sqrt 2))."""
     kind: str = "dense"
     intermediate_size: int = 0
     activation: str = "relu2"
@@ -187,6 +238,23 @@ class RoutedFeedForwardSpec:
     n_groups: int = 1
     keep_groups: int = 1
     correction: bool = True
+    # a bias [n_experts] added to the router's logits (tensor ``router.bias``)
+    router_bias: bool = False
+    # "sigmoid": as above; "softmax_top": the logits choose (with ``correction`` False) and the
+    # chosen experts' weights are the softmax over their logits alone
+    weighting: str = "sigmoid"
+    # an expert of the same form that every token uses, of this width (0: none); its output is
+    # multiplied by sigmoid(w_sg . x), one number per token (tensor ``shared.gate.weight``)
+    shared_size: int = 0
+
+
+@dataclass(frozen=True)
+class LearnedPositionSpec:
+    """A learned vector per position (tensor ``table.weight`` [positions, hidden]) added to the
+    stream after the embedding, times ``scale``."""
+    kind: str = "learned"
+    positions: int = 0
+    scale: float = 1.0
 
 
 @dataclass(frozen=True)

@@ -244,7 +244,7 @@ attention_decode_split_kernel(DecodeArgs a) {
         return;
     }
     const int p = a.positions[b];
-    const int lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
+    const int lo = first_visible(p, a.window);
     const int j0 = lo + split * a.chunk;
     if (j0 > p) return;
     const int n = min(a.chunk, p - j0 + 1);                   // keys of this chunk
@@ -610,7 +610,7 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq,
         return;
     }
     const int p = a.positions[b];
-    const int lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
+    const int lo = first_visible(p, a.window);
     // Tiles this sequence has: from its first key on, or (TMA) the cache pages it touches.
     // A full window in a ring of its own size is the ring's pages, every row of them: the
     // tiles are then counted in ring rows (tile k is the ring's page k), which saves the
@@ -1180,7 +1180,7 @@ void ctas_per_sequence(int resident, int pairs, int most, int* cs, int* clusters
 // window that does not start on one touches one page more, unless it is a ring of its own
 // size.
 int most_tiles(const DecodeArgs& a, bool pages) {
-    return a.n_splits + (pages && a.window > 0 && a.cap != a.window ? 1 : 0);
+    return a.n_splits + (pages && a.window != 0 && a.cap != a.window ? 1 : 0);
 }
 
 template <int HDP, bool TMA>
@@ -1310,7 +1310,7 @@ static int attention_decode_impl(const void* q, long long q_stride, void* out, i
                 "of 16 and at most %d", hd, AD_MAX_HD);
     AGV_REQUIRE(page > 0 && cap > 0 && max_pages > 0 && max_keys > 0,
                 "attention_decode: bad cache geometry");
-    AGV_REQUIRE(window >= 0 && (window == 0 || window <= cap),
+    AGV_REQUIRE(window <= cap,
                 "attention_decode: window %d exceeds the ring of %d rows", window, cap);
     AGV_REQUIRE(agv_aligned(k_pool, 16) && agv_aligned(v_pool, 16),
                 "attention_decode: cache pools must be 16-byte aligned");

@@ -109,7 +109,7 @@ attention_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_st
 
     // visible key range of this query tile: causal end, window start
     const int j_hi = min(m0 + FA_M - 1, len - 1);
-    const int j_lo = window > 0 ? max(0, m0 - window + 1) : 0;
+    const int j_lo = first_visible(m0, window);
     const int t_lo = j_lo / FA_N, t_hi = j_hi / FA_N;
 
     load_tile<HDP, FA_M, FA_THREADS>(Qs, qb, q_stride, m0, len, hd);
@@ -157,7 +157,7 @@ attention_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_st
             for (int e = 0; e < 4; ++e) {
                 const int j = j0 + i * 8 + tig * 2 + (e & 1);
                 const int p = qrow + (e >> 1) * 8;
-                const bool ok = j <= p && j < len && (window <= 0 || j > p - window);
+                const bool ok = j <= p && j < len && j >= first_visible(p, window);
                 float val = -INFINITY;
                 if (ok) {
                     val = s[i][e] * scale_log2e;
@@ -296,7 +296,6 @@ AGV_API int agv_attention_prefill_mma_ex2(const void* q, long long q_stride, con
                 "and row strides that are multiples of 8", hd);
     AGV_REQUIRE(agv_aligned(q, 16) && agv_aligned(k, 16) && agv_aligned(v, 16) &&
                 agv_aligned(out, 4), "attention: operands must be 16-byte aligned");
-    AGV_REQUIRE(window >= 0, "attention: negative window");
     AGV_REQUIRE(B <= 65535 && nh <= 65535, "attention: batch or head count exceeds the grid limit");
     if (B == 0 || max_len == 0) return 0;
     // Four warps (64 query rows) per CTA.  The eight-warp form is kept for

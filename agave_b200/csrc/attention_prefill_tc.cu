@@ -162,7 +162,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
 
     // visible key range of this query tile: causal end, window start
     const int j_hi = min(q0 + a.QT - 1, len - 1);
-    const int j_lo = a.window > 0 ? max(0, q0 - a.window + 1) : 0;
+    const int j_lo = first_visible(q0, a.window);
     const int t_lo = j_lo / AT_N, n_tiles = j_hi / AT_N - t_lo + 1;
 
     if (threadIdx.x == 0) {
@@ -336,13 +336,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
             if (lane == 0) mbar_arrive(&s_free[s]);
             const int j0 = (t_lo + j) * AT_N;
             // a tile every row of the CTA sees whole needs no bounds
-            const bool whole = j0 + AT_N - 1 <= q_min && (a.window <= 0 || j0 > q_max - a.window);
+            const bool whole = j0 + AT_N - 1 <= q_min && j0 >= first_visible(q_max, a.window);
             float sv[64];
             if (whole) {
 #pragma unroll
                 for (int c = 0; c < 64; ++c) sv[c] = __uint_as_float(sr[c >> 4][c & 15]);
             } else {
-                const int lo = a.window > 0 ? qp - a.window : -1;     // visible: lo < key <= qp
+                const int lo = first_visible(qp, a.window) - 1;       // visible: lo < key <= qp
 #pragma unroll
                 for (int c = 0; c < 64; ++c) {
                     const int key = j0 + c;
@@ -608,7 +608,6 @@ AGV_API int agv_attention_prefill_tc_ex2(const void* q, long long q_stride, cons
     AGV_REQUIRE(vt_cols >= agv_attention_prefill_tc_vt_cols(T, B) && vt_cols % 64 == 0,
                 "attention: the transposed-values scratch has %lld columns, %lld are needed",
                 vt_cols, agv_attention_prefill_tc_vt_cols(T, B));
-    AGV_REQUIRE(window >= 0, "attention: negative window");
     AGV_REQUIRE(B <= 65535 && nh <= 65535, "attention: batch or head count exceeds the grid limit");
     if (B == 0 || max_len == 0 || T == 0) return 0;
 

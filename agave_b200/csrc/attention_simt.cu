@@ -62,7 +62,7 @@ attention_simt_kernel(const T* __restrict__ q, long long q_stride, const T* __re
         }
     }
     const int p = positions[t];
-    const int lo = window > 0 ? max(0, p - window + 1) : 0;
+    const int lo = first_visible(p, window);
     const T* qp = q + (size_t)t * q_stride + (size_t)h * hd;
     float qr[AT_MAX_I], acc[AT_MAX_I];
 #pragma unroll
@@ -127,7 +127,6 @@ static int check_attn(int n_tokens, int nh, int nkv, int hd, int window, int hdv
     AGV_REQUIRE(n_tokens >= 0 && nh > 0 && nkv > 0 && hd > 0, "attention: bad sizes");
     AGV_REQUIRE(nh % nkv == 0, "attention: %d heads are not a multiple of %d kv heads", nh, nkv);
     AGV_REQUIRE(hd <= 32 * AT_MAX_I, "attention: head_dim %d exceeds %d", hd, 32 * AT_MAX_I);
-    AGV_REQUIRE(window >= 0, "attention: negative window");
     return 0;
 }
 
@@ -194,7 +193,7 @@ AGV_API int agv_attention_paged_simt_ex(const void* q, long long q_stride, void*
     AGV_REQUIRE(v_row == 0 || v_row >= nkv * hdv, "attention: value rows overlap");
     DistanceBias db{dist_bias, n_dist};
     AGV_REQUIRE(page > 0 && cap > 0 && max_pages > 0, "attention: bad cache geometry");
-    AGV_REQUIRE(window == 0 || window <= cap, "attention: window %d exceeds the ring of %d rows",
+    AGV_REQUIRE(window <= cap, "attention: window %d exceeds the ring of %d rows",
                 window, cap);
     if (n_tokens == 0) return 0;
     const long long items = (long long)n_tokens * nh;

@@ -96,6 +96,17 @@ inline void agv_launch_cluster(void (*kern)(KArgs...), dim3 grid, dim3 block, si
 }
 
 // ---------------------------------------------------------------- element types
+// The first key position a query at position p may see (it sees first..p).  ``window`` W > 0
+// is a sliding window that keeps the last W keys (p - W < j <= p); W < 0 cuts the sequence
+// into blocks of -W positions counted from position 0, and a query sees the keys of its own
+// block only (floor(j / -W) == floor(p / -W)); 0 keeps every key.  The bound never
+// decreases with p.
+__host__ __device__ __forceinline__ int first_visible(int p, int window) {
+    if (window > 0) return p - window + 1 > 0 ? p - window + 1 : 0;
+    if (window < 0) return p - p % (-window);
+    return 0;
+}
+
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
 template <typename T> __device__ __forceinline__ T from_f32(float v);

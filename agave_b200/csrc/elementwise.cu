@@ -40,6 +40,41 @@ AGV_API int agv_embed(const int* tokens, const void* table, int table_dtype, flo
     return 0;
 }
 
+// ------------------------------------------------- learned position vectors
+// out[t, :] += table[positions[t], :] * scale: a learned vector per position joins the
+// 32-bit stream.  A position outside the table adds nothing (callers bound the context).
+template <typename TW>
+__global__ void add_rows_kernel(const int* __restrict__ positions, const TW* __restrict__ table,
+                                float* __restrict__ out, int H, int rows, float scale) {
+    pdl_wait();
+    pdl_launch_next();
+    const int t = blockIdx.x;
+    const int p = positions[t];
+    if (p < 0 || p >= rows) return;
+    const TW* row = table + (size_t)p * H;
+    float* o = out + (size_t)t * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] += to_f32(row[i]) * scale;
+}
+
+AGV_API int agv_add_position_rows(const int* positions, const void* table, int table_dtype,
+                                  float* out, int T, int H, int rows, float scale,
+                                  cudaStream_t stream) {
+    AGV_REQUIRE(T >= 0 && H > 0 && rows > 0, "add_position_rows: bad sizes T=%d H=%d rows=%d", T,
+                H, rows);
+    if (T == 0) return 0;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (table_dtype == AGV_F32)
+        agv_launch(add_rows_kernel<float>, T, threads, 0, stream, positions, (const float*)table,
+                   out, H, rows, scale);
+    else if (table_dtype == AGV_BF16)
+        agv_launch(add_rows_kernel<__nv_bfloat16>, T, threads, 0, stream, positions,
+                   (const __nv_bfloat16*)table, out, H, rows, scale);
+    else
+        return agv_fail(-1, "add_position_rows: unknown dtype %d", table_dtype);
+    AGV_LAUNCH_OK("add_rows_kernel");
+    return 0;
+}
+
 // ------------------------------------------------------------ rotation tables
 __global__ void rope_table_kernel(const int* __restrict__ positions, float* __restrict__ cosv,
                                   float* __restrict__ sinv, int T, int half, double log_theta,

@@ -1,7 +1,7 @@
 // Matrix products on the ordinary arithmetic units: out[M, N] = x[M, K] * w[N, K]^T,
 // and the gated pair act(x wg^T) * (x wu^T).  This is the whole 32-bit path
 // (plain FFMA, no reduced-precision mode) and the fallback of the bfloat16 path
-// for shapes the tensor-core kernel refuses.  A plain product may carry the squared relu.
+// for shapes the tensor-core kernel refuses.  A plain product may carry the squared relu or the erf GELU.
 //
 // Each output element is one dot product accumulated over k in ascending order
 // in 32-bit, whatever M and N are, so a row's result does not depend on which
@@ -12,8 +12,9 @@
 // activation src/backend/kernels/cuda/gelu_mul.zig:12-19 (here with tanhf).
 #include "common.cuh"
 
-// (the squared relu, max(t, 0)^2, goes with the plain product only)
-enum AgvActivation { AGV_ACT_GELU_TANH = 0, AGV_ACT_SILU = 1, AGV_ACT_RELU2 = 2 };
+// (the squared relu, max(t, 0)^2, and the erf GELU, t/2 (1 + erf(t / sqrt 2)), go with the
+// plain product only)
+enum AgvActivation { AGV_ACT_GELU_TANH = 0, AGV_ACT_SILU = 1, AGV_ACT_RELU2 = 2, AGV_ACT_GELU_ERF = 3 };
 
 __device__ __forceinline__ float gelu_tanh_f(float t) {
     const float u = 0.7978845608028654f * (t + 0.044715f * t * t * t);
@@ -84,6 +85,7 @@ gemm_tn_kernel(const TA* __restrict__ A, const TW* __restrict__ W, const TW* __r
             float v = acc[i][j];
             if (GATED) v = activate(v, act) * acc2[i][j];
             else if (act == AGV_ACT_RELU2) { v = fmaxf(v, 0.f); v *= v; }
+            else if (act == AGV_ACT_GELU_ERF) v = 0.5f * v * (1.0f + erff(v * 0.7071067811865476f));
             C[(size_t)m * ldc + n] = from_f32<TO>(v);
         }
     }
@@ -109,7 +111,7 @@ AGV_API int agv_linear_simt(const void* x, const void* w, const void* w2, void* 
                             int act, cudaStream_t stream) {
     AGV_REQUIRE(M >= 0 && N > 0 && K > 0, "linear: bad sizes M=%d N=%d K=%d", M, N, K);
     AGV_REQUIRE(lda >= K && ldc >= N, "linear: row strides %lld, %lld shorter than rows", lda, ldc);
-    AGV_REQUIRE(act != AGV_ACT_RELU2 || !w2, "linear: the squared relu goes with a plain product");
+    AGV_REQUIRE(act < AGV_ACT_RELU2 || !w2, "linear: the squared relu and the erf GELU go with a plain product");
     AGV_REQUIRE((long long)((M + BM - 1) / BM) <= 65535, "linear: M=%d exceeds the grid limit", M);
     if (M == 0) return 0;
     if (in_dtype == AGV_F32 && out_dtype == AGV_F32)

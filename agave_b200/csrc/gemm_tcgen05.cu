@@ -70,6 +70,11 @@ __device__ __forceinline__ float gelu_tanh_fast(float t) {
     return 0.5f * t * (1.0f + th);
 }
 __device__ __forceinline__ float silu_fast(float t) { return __fdividef(t, 1.0f + __expf(-t)); }
+// The activation a plain product may carry: 2 the squared relu, 3 the erf GELU.
+__device__ __forceinline__ float plain_act(float t, int act) {
+    if (act == 2) { t = fmaxf(t, 0.f); return t * t; }
+    return 0.5f * t * (1.0f + erff(t * 0.7071067811865476f));
+}
 
 // MODE 0: plain.  MODE 1: gated, gate and up tiles of 128 rows each with an
 // accumulator of their own (prompts).  MODE 2: gated, 64 gate rows and the 64 up
@@ -361,7 +366,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
                         float v = __uint_as_float(r[j]);
                         if (GATED)
                             v = (act == 1 ? silu_fast(v) : gelu_tanh_fast(v)) * __uint_as_float(u[j]);
-                        else if (MODE == 0 && act == 2) { v = fmaxf(v, 0.f); v *= v; }   // squared relu
+                        else if (MODE == 0 && act >= 2) v = plain_act(v, act);
                         store_out<TO>(ctile + (c + j) * TILE_M + fl, v);
                     }
                 }
@@ -445,7 +450,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
                         if (HALF) up += inbox[((size_t)q * BN + n) * rows + per + jl];
                     }
                     if (HALF) acc = (act == 1 ? silu_fast(acc) : gelu_tanh_fast(acc)) * up;
-                    else if (MODE == 0 && act == 2) { acc = fmaxf(acc, 0.f); acc *= acc; }
+                    else if (MODE == 0 && act >= 2) acc = plain_act(acc, act);
                     store_out<TO>(gout + (size_t)(n0 + n) * ldc + m0 + fl, acc);
                 }
             }
@@ -472,9 +477,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
 #pragma unroll
                         for (int q = 0; q < 8; ++q) up += pu[q];
                         acc = (act == 1 ? silu_fast(acc) : gelu_tanh_fast(acc)) * up;
-                    } else if (MODE == 0 && act == 2) {
-                        acc = fmaxf(acc, 0.f);
-                        acc *= acc;
+                    } else if (MODE == 0 && act >= 2) {
+                        acc = plain_act(acc, act);
                     }
                     store_out<TO>(gout + (size_t)(n0 + n) * ldc + m0 + fl, acc);
                 }
@@ -929,13 +933,11 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w,
                                           gelu_tanh_fast(__uint_as_float(r[j])) *
                                               __uint_as_float(u[j]));
                     }
-                } else if (MODE == 0 && act == 2) {
-                    // plain product with the squared relu on it
+                } else if (MODE == 0 && act >= 2) {
+                    // plain product with an activation on it
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const float v = fmaxf(__uint_as_float(r[j]), 0.f);
-                        store_out<TO>(wst + j * 32 + lane, v * v);
-                    }
+                    for (int j = 0; j < 16; ++j)
+                        store_out<TO>(wst + j * 32 + lane, plain_act(__uint_as_float(r[j]), act));
                 } else {
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
@@ -1447,10 +1449,11 @@ AGV_API int agv_linear_tc(const void* x, const void* w, const void* w2, void* ou
                 "linear: operands must be 16-byte aligned");
     AGV_REQUIRE(lda >= K && ldc >= N, "linear: row strides shorter than rows");
     AGV_REQUIRE(splits >= 1, "linear: splits must be >= 1");
-    // act 2 (the squared relu) belongs to the plain product and needs a finished sum
-    AGV_REQUIRE(act != 2 || (!w2 && (splits == 1 || splits == cluster)),
-                "linear: the squared relu goes with a plain product whose sum is finished in the "
-                "kernel (one range of K, or one cluster's)");
+    // act 2 (the squared relu) and 3 (the erf GELU) belong to the plain product and need a
+    // finished sum
+    AGV_REQUIRE(act < 2 || (!w2 && (splits == 1 || splits == cluster)),
+                "linear: the squared relu and the erf GELU go with a plain product whose sum is "
+                "finished in the kernel (one range of K, or one cluster's)");
     AGV_REQUIRE(splits == 1 || !w2 || (cluster == splits && T <= 64),
                 "linear: the gated form splits K only over one cluster and for at most 64 tokens");
     AGV_REQUIRE(cluster == 0 || (cluster >= 2 && cluster <= 8 && splits % cluster == 0),

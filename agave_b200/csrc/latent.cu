@@ -4,7 +4,9 @@
 //
 //  * whole-projection norm (agv_proj_norm_store): the row is q | k | v; q and k are each
 //    RMS-normed over their WHOLE width (all heads at once, a weight of that width), v is
-//    taken as it is; k and v go to the paged cache.
+//    taken as it is or, with v_first [T, nv] and a weight m, as (1 - m) v + m v_first (the
+//    values of an earlier layer for the same tokens, mixed in 32-bit before the one
+//    rounding); k and v go to the paged cache.
 //  * latent attention (agv_latent_prepare): the row is Q | c | kr | g.  c (the key/value
 //    latent) is RMS-normed, kr (one rotated key part shared by all heads) is rotated by
 //    position, and c | kr is the cache row of the position.  Q is either the queries
@@ -22,63 +24,9 @@
 // the sigmoid are 32-bit whatever the row's dtype.
 #include "common.cuh"
 #include "cache_write.cuh"
+#include "row_in.cuh"
 
 namespace {
-
-// The input row of token t: 32-bit partial sums [n_splits, T, W] or the row itself.
-template <typename T>
-struct RowIn {
-    const T* row;              // [T, ld] or null
-    long long ld;
-    const float* part;         // [n_splits, T, W] or null
-    int n_splits;
-    long long split_stride;
-    int W;
-    __device__ __forceinline__ float at(int t, int e) const {
-        if (part) {
-            float s = 0.f;
-            const float* p = part + (size_t)t * W + e;
-            for (int sp = 0; sp < n_splits; ++sp) s += p[(size_t)sp * split_stride];
-            return s;
-        }
-        return to_f32(row[(size_t)t * ld + e]);
-    }
-    // The whole row of token t into shared memory, 32-bit: eight values per thread at a
-    // time with all their loads issued before the first is used (a dependent trip to L2 or
-    // HBM costs about a microsecond, and a decode step has few rows to hide it behind).
-    __device__ __forceinline__ void load(int t, float* buf) const {
-        for (int e0 = threadIdx.x; e0 < W; e0 += blockDim.x * 8) {
-            float v[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] = 0.f;
-            if (part) {
-                const float* p = part + (size_t)t * W;
-#pragma unroll 4
-                for (int sp = 0; sp < n_splits; ++sp) {
-                    const float* ps = p + (size_t)sp * split_stride;
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const int e = e0 + i * blockDim.x;
-                        if (e < W) v[i] += ps[e];
-                    }
-                }
-            } else {
-                const T* r = row + (size_t)t * ld;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int e = e0 + i * blockDim.x;
-                    if (e < W) v[i] = to_f32(r[e]);
-                }
-            }
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int e = e0 + i * blockDim.x;
-                if (e < W) buf[e] = v[i];
-            }
-        }
-        __syncthreads();
-    }
-};
 
 // Cache row of token t, or null when nothing is stored for it (padding, or a ring row that
 // a later token of the same step overwrites).
@@ -106,7 +54,8 @@ template <typename T>
 __global__ void __launch_bounds__(1024)
 proj_norm_store_kernel(RowIn<T> in, T* __restrict__ out, long long ldo, int n_tokens, int nq,
                        int nk, int nv, const float* __restrict__ wq, const float* __restrict__ wk,
-                       float eps, const int* __restrict__ positions, CacheWrite cw) {
+                       float eps, const int* __restrict__ positions, CacheWrite cw,
+                       const T* __restrict__ v_first, long long ldvf, float v_mix) {
     pdl_wait();
     pdl_launch_next();
     extern __shared__ float buf[];           // the row, 32-bit
@@ -130,6 +79,8 @@ proj_norm_store_kernel(RowIn<T> in, T* __restrict__ out, long long ldo, int n_to
         float v = buf[e];
         if (e < nq) v = v * rq * wq[e];
         else if (e < nq + nk) v = v * rk * wk[e - nq];
+        else if (v_first)      // the values lean towards an earlier layer's of the same token
+            v = (1.0f - v_mix) * v + v_mix * to_f32(v_first[(size_t)t * ldvf + e - nq - nk]);
         const T r = from_f32<T>(v);
         o[e] = r;
         if (e >= nq + nk) { if (vc) vc[e - nq - nk] = r; }
@@ -438,13 +389,17 @@ AGV_API int agv_rope_table_freqs(const int* positions, const double* freqs, floa
 // row: [T, W] with row stride ld (dtype), or part: [n_splits, T, W] 32-bit partial sums
 // (row may then be null).  out: [T, W] with row stride ldo (may be row itself).  W = nq + nk
 // + nv.  wq [nq], wk [nk]: 32-bit.  Pools (may be null): rows of nk and nv elements.
+// v_first (may be null): [T, nv] with row stride ldvf, in the row's dtype; v_mix its weight.
 AGV_API int agv_proj_norm_store(const void* row, long long ld, const float* part, int n_splits,
                                 void* out, long long ldo, int dtype, int T, int nq, int nk, int nv,
                                 const float* wq, const float* wk, float eps, const int* positions,
                                 void* k_pool, void* v_pool, const int* page_table,
                                 const int* slots, const int* lens, const int* seq_index,
-                                int max_pages, int page, int cap, cudaStream_t stream) {
+                                int max_pages, int page, int cap, const void* v_first,
+                                long long ldvf, float v_mix, cudaStream_t stream) {
     AGV_REQUIRE(T >= 0 && nq > 0 && nk >= 0 && nv >= 0, "proj_norm: bad sizes");
+    AGV_REQUIRE(!v_first || (ldvf >= nv && v_first != out), "proj_norm: the values to mix in need "
+                "rows of their own, at least as wide as the values");
     AGV_REQUIRE(row || part, "proj_norm: no input");
     AGV_REQUIRE(wq && (nk == 0 || wk), "proj_norm: norm weights are missing");
     AGV_REQUIRE(!k_pool || (page_table && slots && lens && seq_index && page > 0 && cap > 0),
@@ -463,7 +418,7 @@ AGV_API int agv_proj_norm_store(const void* row, long long ld, const float* part
             AGV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                              (int)smem));                                       \
         agv_launch(kern, (unsigned)T, row_threads(T), smem, stream, in, (TT*)out, ldo, T, nq,   \
-                   nk, nv, wq, wk, eps, positions, cw);                                         \
+                   nk, nv, wq, wk, eps, positions, cw, (const TT*)v_first, ldvf, v_mix);        \
     } while (0)
     if (dtype == AGV_F32) AGV_PN(float);
     else if (dtype == AGV_BF16) AGV_PN(__nv_bfloat16);

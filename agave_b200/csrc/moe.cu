@@ -7,6 +7,9 @@
 // expert is masked out before the top-k, whatever the sign of the scores); the `top`
 // largest c among them win, and their weights are their s, unchanged.  n_groups = keep = 1
 // is plain top-k routing; correction null adds nothing.  Ties go to the lower index.
+// Two options: a bias [E] added to the logits (z = W_r x + b), and weights that are the
+// softmax over the chosen experts' logits alone (the logits then also make the choice)
+// instead of their sigmoids.
 //
 // Plan: the P = T * top pairs are laid out by expert, every expert's run padded to a
 // multiple of the row tile, so that a tile of the grouped products belongs to one expert.
@@ -33,10 +36,31 @@ __device__ __forceinline__ float moe_act(float t, int act) {
 constexpr int RT_WARPS = 4;
 constexpr int RT_MAX_E = 512;
 
+// How a logit becomes a score: bias [E] (or null) is added to it first; softmax_top: the
+// score is the logit itself and the chosen experts' weights are the softmax over their
+// logits, else the score, and the weight, is the logit's sigmoid.
+struct RouteScore {
+    const float* bias;
+    int softmax_top;
+    __device__ __forceinline__ float score(float z, int e) const {
+        if (bias) z += bias[e];
+        return softmax_top ? z : 1.0f / (1.0f + expf(-z));
+    }
+    // the chosen experts' scores (their logits) become their softmax, by one thread
+    __device__ __forceinline__ void weigh(float* w, int top) const {
+        if (!softmax_top) return;
+        float m = w[0];
+        for (int k = 1; k < top; ++k) m = fmaxf(m, w[k]);
+        float sum = 0.f;
+        for (int k = 0; k < top; ++k) { w[k] = expf(w[k] - m); sum += w[k]; }
+        for (int k = 0; k < top; ++k) w[k] /= sum;
+    }
+};
+
 // The choice of one token from its scores (one thread): s [E] sigmoid scores, c [E] choice
 // scores (consumed).
 __device__ void moe_choose(float* s, float* c, int E, int n_groups, int keep, int top,
-                           int* __restrict__ ids, float* __restrict__ wts) {
+                           int* __restrict__ ids, float* __restrict__ wts, RouteScore rs) {
     const int per = E / n_groups;
     if (keep < n_groups) {
         // group scores: the two largest choice scores of each group, summed
@@ -73,6 +97,7 @@ __device__ void moe_choose(float* s, float* c, int E, int n_groups, int keep, in
         wts[k] = s[best];
         c[best] = -INFINITY;
     }
+    rs.weigh(wts, top);
 }
 
 // Index of the greatest of v[0..n) over a warp (the lowest index among equals; -1 if all are
@@ -96,7 +121,7 @@ __device__ __forceinline__ int warp_argmax(const float* v, int n, int lane) {
 // The same choice made by a whole warp: gs [n_groups] is scratch for the group scores.
 __device__ void moe_choose_warp(float* s, float* c, float* gs, int E, int n_groups, int keep,
                                 int top, int* __restrict__ ids, float* __restrict__ wts,
-                                int lane) {
+                                int lane, RouteScore rs) {
     const int per = E / n_groups;
     if (keep < n_groups) {
         for (int g = lane; g < n_groups; g += 32) {
@@ -137,6 +162,7 @@ __device__ void moe_choose_warp(float* s, float* c, float* gs, int E, int n_grou
         }
         __syncwarp();
     }
+    if (lane == 0) rs.weigh(wts, top);
 }
 
 // One warp per token: logits by lanes over H, then lane 0 chooses.  The general form (any
@@ -145,7 +171,8 @@ template <typename T>
 __global__ void __launch_bounds__(RT_WARPS * 32)
 moe_route_kernel(const T* __restrict__ x, long long ldx, const T* __restrict__ wr,
                  const float* __restrict__ correction, int n_tokens, int H, int E, int n_groups,
-                 int keep, int top, int* __restrict__ ids, float* __restrict__ wts) {
+                 int keep, int top, int* __restrict__ ids, float* __restrict__ wts,
+                 RouteScore rs) {
     pdl_wait();
     pdl_launch_next();
     extern __shared__ float smem[];
@@ -161,14 +188,14 @@ moe_route_kernel(const T* __restrict__ x, long long ldx, const T* __restrict__ w
         for (int i = lane; i < H; i += 32) z = fmaf(to_f32(xr[i]), to_f32(w[i]), z);
         z = warp_sum(z);
         if (lane == 0) {
-            const float sg = 1.0f / (1.0f + expf(-z));
+            const float sg = rs.score(z, e);
             s[e] = sg;
             c[e] = sg + (correction ? correction[e] : 0.f);
         }
     }
     __syncwarp();
     if (lane == 0)
-        moe_choose(s, c, E, n_groups, keep, top, ids + (size_t)t * top, wts + (size_t)t * top);
+        moe_choose(s, c, E, n_groups, keep, top, ids + (size_t)t * top, wts + (size_t)t * top, rs);
 }
 
 // 16 bytes of a row as 32-bit values.
@@ -204,7 +231,7 @@ __global__ void __launch_bounds__(RT_VW * 32)
 moe_route_tiled_kernel(const T* __restrict__ x, long long ldx, const T* __restrict__ wr,
                        const float* __restrict__ correction, int n_tokens, int H, int E,
                        int n_groups, int keep, int top, int* __restrict__ ids,
-                       float* __restrict__ wts) {
+                       float* __restrict__ wts, RouteScore rs) {
     pdl_wait();
     pdl_launch_next();
     extern __shared__ float smem[];              // [RT_TOK][3][E]
@@ -233,7 +260,7 @@ moe_route_tiled_kernel(const T* __restrict__ x, long long ldx, const T* __restri
         for (int k = 0; k < RT_TOK; ++k) {
             const float zz = warp_sum(z[k]);
             if (lane == 0) {
-                const float sg = 1.0f / (1.0f + expf(-zz));
+                const float sg = rs.score(zz, e);
                 smem[(k * 3) * E + e] = sg;
                 smem[(k * 3 + 1) * E + e] = sg + (correction ? correction[e] : 0.f);
             }
@@ -244,7 +271,7 @@ moe_route_tiled_kernel(const T* __restrict__ x, long long ldx, const T* __restri
         const int t = t0 + warp;
         moe_choose_warp(smem + (warp * 3) * E, smem + (warp * 3 + 1) * E,
                         smem + (warp * 3 + 2) * E, E, n_groups, keep, top, ids + (size_t)t * top,
-                        wts + (size_t)t * top, lane);
+                        wts + (size_t)t * top, lane, rs);
     }
 }
 
@@ -396,9 +423,13 @@ moe_grouped_kernel(const TA* __restrict__ A, long long lda, const int* __restric
 
 // x: [T, H] rows of stride ldx, wr: [E, H] (both `dtype`); correction: [E] 32-bit or null;
 // ids, wts: [T, top] outputs.
-AGV_API int agv_moe_route(const void* x, long long ldx, const void* wr, const float* correction,
-                          int dtype, int T, int H, int E, int n_groups, int keep, int top,
-                          int* ids, float* wts, cudaStream_t stream) {
+// bias: [E] 32-bit or null, added to the logits; softmax_top != 0: the logits choose and the
+// weights are the softmax over the chosen logits (else sigmoids, see the head of this file).
+AGV_API int agv_moe_route_ex(const void* x, long long ldx, const void* wr,
+                             const float* correction, const float* bias, int softmax_top,
+                             int dtype, int T, int H, int E, int n_groups, int keep, int top,
+                             int* ids, float* wts, cudaStream_t stream) {
+    const RouteScore rs{bias, softmax_top};
     AGV_REQUIRE(T >= 0 && H > 0 && E > 0 && top > 0, "moe_route: bad sizes");
     AGV_REQUIRE(E <= RT_MAX_E, "moe_route: %d experts exceed %d", E, RT_MAX_E);
     AGV_REQUIRE(n_groups >= 1 && E % n_groups == 0, "moe_route: %d experts do not form %d equal "
@@ -414,7 +445,7 @@ AGV_API int agv_moe_route(const void* x, long long ldx, const void* wr, const fl
 #define AGV_ROUTE(TT, TOK, VW)                                                                  \
     agv_launch(moe_route_tiled_kernel<TT, TOK, VW>, (unsigned)((T + TOK - 1) / TOK), VW * 32,   \
                (size_t)TOK * 3 * E * sizeof(float), stream, (const TT*)x, ldx, (const TT*)wr,   \
-               correction, T, H, E, n_groups, keep, top, ids, wts)
+               correction, T, H, E, n_groups, keep, top, ids, wts, rs)
         if (T <= 64) {
             if (dtype == AGV_F32) AGV_ROUTE(float, 1, 16);
             else AGV_ROUTE(__nv_bfloat16, 1, 16);
@@ -430,14 +461,59 @@ AGV_API int agv_moe_route(const void* x, long long ldx, const void* wr, const fl
     const size_t smem = (size_t)RT_WARPS * 2 * E * sizeof(float);
     if (dtype == AGV_F32)
         agv_launch(moe_route_kernel<float>, grid, RT_WARPS * 32, smem, stream, (const float*)x, ldx,
-                   (const float*)wr, correction, T, H, E, n_groups, keep, top, ids, wts);
+                   (const float*)wr, correction, T, H, E, n_groups, keep, top, ids, wts, rs);
     else if (dtype == AGV_BF16)
         agv_launch(moe_route_kernel<__nv_bfloat16>, grid, RT_WARPS * 32, smem, stream,
                    (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)wr, correction, T, H, E,
-                   n_groups, keep, top, ids, wts);
+                   n_groups, keep, top, ids, wts, rs);
     else
         return agv_fail(-1, "moe_route: unknown dtype %d", dtype);
     AGV_LAUNCH_OK("moe_route_kernel");
+    return 0;
+}
+
+AGV_API int agv_moe_route(const void* x, long long ldx, const void* wr, const float* correction,
+                          int dtype, int T, int H, int E, int n_groups, int keep, int top,
+                          int* ids, float* wts, cudaStream_t stream) {
+    return agv_moe_route_ex(x, ldx, wr, correction, nullptr, 0, dtype, T, H, E, n_groups, keep,
+                            top, ids, wts, stream);
+}
+
+// y [T, H] (32-bit) *= sigmoid(x[t, :] . w) per row t: one gate value per token for a branch
+// that runs for every token.  x: [T, K] rows of stride ldx, w: [K] (both `dtype`); the dot
+// product and the sigmoid are 32-bit.
+namespace {
+template <typename T>
+__global__ void __launch_bounds__(128)
+row_gate_kernel(const T* __restrict__ x, long long ldx, const T* __restrict__ w,
+                float* __restrict__ y, int K, int H) {
+    pdl_wait();
+    pdl_launch_next();
+    __shared__ float red[33];
+    const int t = blockIdx.x;
+    const T* xr = x + (size_t)t * ldx;
+    float z = 0.f;
+    for (int i = threadIdx.x; i < K; i += blockDim.x) z = fmaf(to_f32(xr[i]), to_f32(w[i]), z);
+    z = block_sum(z, red);
+    const float g = 1.0f / (1.0f + expf(-z));
+    float* yr = y + (size_t)t * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) yr[i] *= g;
+}
+}  // namespace
+
+AGV_API int agv_row_gate(const void* x, long long ldx, const void* w, int dtype, float* y, int T,
+                         int K, int H, cudaStream_t stream) {
+    AGV_REQUIRE(T >= 0 && K > 0 && H > 0 && ldx >= K, "row_gate: bad sizes");
+    if (T == 0) return 0;
+    if (dtype == AGV_F32)
+        agv_launch(row_gate_kernel<float>, (unsigned)T, 128, 0, stream, (const float*)x, ldx,
+                   (const float*)w, y, K, H);
+    else if (dtype == AGV_BF16)
+        agv_launch(row_gate_kernel<__nv_bfloat16>, (unsigned)T, 128, 0, stream,
+                   (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, y, K, H);
+    else
+        return agv_fail(-1, "row_gate: unknown dtype %d", dtype);
+    AGV_LAUNCH_OK("row_gate_kernel");
     return 0;
 }
 

@@ -43,6 +43,9 @@ class StepContext:
     lens_host: object = None      # the lengths on the host, when per-operation timing wants them
     rope_tables: Dict[Tuple, Tuple[torch.Tensor, torch.Tensor]] = field(default_factory=dict)
     step_kv: Dict[int, Tuple] = field(default_factory=dict)
+    # what a layer keeps for later layers of the same step, by its cache entry (the values
+    # another layer mixes into its own)
+    step_values: Dict[int, torch.Tensor] = field(default_factory=dict)
 
     def new(self, *shape, dtype=None) -> torch.Tensor:
         return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)

@@ -18,7 +18,7 @@ from . import perf as _perf_mod
 from .csrc import build as _build
 
 F32, BF16 = 0, 1
-ACT = {"gelu_tanh": 0, "silu": 1, "relu2": 2}     # relu2: on a plain product only
+ACT = {"gelu_tanh": 0, "silu": 1, "relu2": 2, "gelu_erf": 3}   # 2, 3: on a plain product only
 
 _lib = None
 _lock = threading.Lock()
@@ -137,6 +137,19 @@ def embed(tokens: torch.Tensor, table: torch.Tensor, scale: float, out: torch.Te
     with _span("embed", T * H * table.element_size() + _nbytes(out)):
         _check(library().agv_embed(_ptr(tokens), _ptr(table), dtype_code(table.dtype), _ptr(out),
                                    T, H, V, ctypes.c_float(scale), _stream()))
+
+
+def add_position_rows(positions: torch.Tensor, table: torch.Tensor, out: torch.Tensor,
+                      scale: float = 1.0) -> None:
+    """out[t, :] += table[positions[t], :] * scale (out 32-bit): a learned vector per
+    position joins the stream."""
+    _i32(positions, "positions"); _f32(out, "out"); _dense(table, "table"); _dense(out, "out")
+    T, (R, H) = positions.numel(), table.shape
+    assert out.shape == (T, H)
+    with _span("embed", T * H * table.element_size() + 2 * _nbytes(out)):
+        _check(library().agv_add_position_rows(_ptr(positions), _ptr(table),
+                                               dtype_code(table.dtype), _ptr(out), T, H, R,
+                                               ctypes.c_float(scale), _stream()))
 
 
 def rope_table(positions: torch.Tensor, rotary_dim: int, theta: float, factor: float,
@@ -262,21 +275,36 @@ def soft_cap(z: torch.Tensor, cap: float) -> None:
 
 # ------------------------------------------------------ routed feed-forward
 def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor],
-              n_groups: int, keep: int, top: int, ids: torch.Tensor, wts: torch.Tensor) -> None:
+              n_groups: int, keep: int, top: int, ids: torch.Tensor, wts: torch.Tensor,
+              bias: Optional[torch.Tensor] = None, softmax_top: bool = False) -> None:
     """ids, wts [T, top]: the experts each token of x [T, H] uses and their weights.
     s = sigmoid(W_r x) in 32-bit; s + correction chooses (only among the experts of the
     ``keep`` groups, of ``n_groups`` equal ones, whose two largest choice scores sum highest),
-    s itself weighs."""
+    s itself weighs.  ``bias`` [E] (32-bit) is added to the logits first; ``softmax_top``: the
+    logits themselves choose and the weights are the softmax over the chosen logits."""
     T, H = x.shape
     E = w_router.shape[0]
     assert w_router.shape == (E, H) and x.stride(1) == 1 and x.dtype == w_router.dtype
     _dense(w_router, "w_router"); _f32(correction, "correction"); _i32(ids, "ids"); _f32(wts, "wts")
-    _dense(ids, "ids"); _dense(wts, "wts")
+    _dense(ids, "ids"); _dense(wts, "wts"); _f32(bias, "bias")
     assert ids.shape == (T, top) and wts.shape == (T, top)
+    assert bias is None or bias.shape == (E,)
     with _span("router", _nbytes(x, w_router), 2 * T * E * H):
-        _check(library().agv_moe_route(_ptr(x), ctypes.c_longlong(x.stride(0)), _ptr(w_router),
-                                       _ptr(correction), dtype_code(x.dtype), T, H, E, n_groups,
-                                       keep, top, _ptr(ids), _ptr(wts), _stream()))
+        _check(library().agv_moe_route_ex(_ptr(x), ctypes.c_longlong(x.stride(0)), _ptr(w_router),
+                                          _ptr(correction), _ptr(bias), 1 if softmax_top else 0,
+                                          dtype_code(x.dtype), T, H, E, n_groups, keep, top,
+                                          _ptr(ids), _ptr(wts), _stream()))
+
+
+def row_gate(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor) -> None:
+    """y [T, H] (32-bit) *= sigmoid(x[t, :] . w) row by row: one gate value per token."""
+    T, K = x.shape
+    assert w.numel() == K and w.dtype == x.dtype and x.stride(1) == 1
+    _f32(y, "y"); _dense(y, "y"); _dense(w, "w")
+    assert y.shape[0] == T and y.dim() == 2
+    with _span("gate", 2 * _nbytes(y) + _nbytes(x)):
+        _check(library().agv_row_gate(_ptr(x), ctypes.c_longlong(x.stride(0)), _ptr(w),
+                                      dtype_code(x.dtype), _ptr(y), T, K, y.shape[1], _stream()))
 
 
 class MoePlan:
@@ -613,11 +641,13 @@ def _row_input(row, partial, T, W):
 
 def proj_norm_store(out: torch.Tensor, nq: int, nk: int, nv: int, wq: torch.Tensor,
                     wk: torch.Tensor, eps: float, positions: torch.Tensor, view=None, ctx=None,
-                    partial: Optional[torch.Tensor] = None) -> None:
+                    partial: Optional[torch.Tensor] = None,
+                    v_first: Optional[torch.Tensor] = None, v_mix: float = 0.0) -> None:
     """out [T, nq + nk + nv] = q | k | v of a stacked projection with q and k each RMS-normed
     over their whole width (weights wq [nq], wk [nk], 32-bit); the input is ``partial``
     ([S, T, W] 32-bit partial sums) or out itself.  With ``view`` (a cache entry's pools) the
-    k and v parts also go to the cache rows of the tokens' positions."""
+    k and v parts also go to the cache rows of the tokens' positions.  With ``v_first``
+    [T, nv] (rows of another tensor) the values become (1 - v_mix) v + v_mix v_first."""
     T, W = out.shape
     assert W == nq + nk + nv and out.stride(1) == 1
     _f32(wq, "wq"); _f32(wk, "wk"); _i32(positions, "positions")
@@ -625,11 +655,15 @@ def proj_norm_store(out: torch.Tensor, nq: int, nk: int, nv: int, wq: torch.Tens
     cache = _cache_args(view, ctx)
     if view is not None:
         assert view.k_pool.dtype == out.dtype
+    if v_first is not None:
+        assert v_first.shape == (T, nv) and v_first.stride(1) == 1 and v_first.dtype == out.dtype
     with _span("qk_norm_rope", 2 * _nbytes(out) + _nbytes(partial)):
         _check(library().agv_proj_norm_store(
             rp, ctypes.c_longlong(ld), pp, ns, _ptr(out), ctypes.c_longlong(out.stride(0)),
             dtype_code(out.dtype), T, nq, nk, nv, _ptr(wq), _ptr(wk), ctypes.c_float(eps),
-            _ptr(positions), *cache, _stream()))
+            _ptr(positions), *cache, _ptr(v_first),
+            ctypes.c_longlong(v_first.stride(0) if v_first is not None else 0),
+            ctypes.c_float(v_mix), _stream()))
 
 
 def latent_prepare(out: torch.Tensor, q_width: int, q_latent: bool, heads: int, d: int, r: int,
@@ -733,8 +767,8 @@ def relu2(z: torch.Tensor) -> None:
 
 def linear_activated(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, activation: str,
                      op: str = "linear") -> None:
-    """out = act(x w^T); "relu2" is the squared relu."""
-    if activation != "relu2":
+    """out = act(x w^T); "relu2" is the squared relu, "gelu_erf" the erf GELU."""
+    if activation not in ("relu2", "gelu_erf"):
         raise KernelError(f"linear_activated: unknown activation {activation!r}")
     # the activation is the product's epilogue, where the sum is finished: one range of K, or
     # (decoding through a layer with few row tiles) the ranges of one cluster
@@ -746,6 +780,80 @@ def linear_activated(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, activa
         linear_tc(x, w, out, None, activation, splits=max(c, 1), cluster=c, op=op)
     else:
         linear_simt(x, w, out, None, activation, op=op)
+
+
+# ------------------------------------------------------- gated delta rule
+def _state_args(state: torch.Tensor):
+    """(pointer, row stride) of a fixed-size state [n_slots, numel]."""
+    _f32(state, "state")
+    assert state.dim() == 2 and state.stride(1) == 1
+    return _ptr(state), ctypes.c_longlong(state.stride(0))
+
+
+def delta_prepare(row: Optional[torch.Tensor], partial: Optional[torch.Tensor], T: int, ctx,
+                  state: torch.Tensor, conv_off: int, n_qk_heads: int, n_heads: int,
+                  head_dim: int, value_dim: int, taps: int, decay_rank: int, gate_rank: int,
+                  conv_w: torch.Tensor, unit_eps: float, q_mult: float, qkv: torch.Tensor,
+                  beta: torch.Tensor, low_a: torch.Tensor, low_g: torch.Tensor) -> None:
+    """From a token's row  q | k | v | b | a1 | g1  of the stacked projection ([T, W] in the
+    compute dtype or ``partial`` [S, T, W] 32-bit sums): the causal convolution over ``taps``
+    tokens and silu on q, k and v (its earlier inputs come from the step's rows or, before
+    the step, from ``state`` at ``conv_off``, which is brought up to date), unit q and k heads
+    (q times ``q_mult``), beta = sigmoid(b).  qkv [T, 2 G d + H dv] and beta [T, H] are 32-bit;
+    low_a [T, ra] and low_g [T, rg] are the two bottlenecks in the compute dtype."""
+    C = 2 * n_qk_heads * head_dim + n_heads * value_dim
+    W = C + n_heads + decay_rank + gate_rank
+    rp, ld, pp, ns = _row_input(row, partial, T, W)
+    _f32(conv_w, "conv_w"); _dense(conv_w, "conv_w"); _f32(qkv, "qkv"); _f32(beta, "beta")
+    _dense(qkv, "qkv"); _dense(beta, "beta"); _dense(low_a, "low_a"); _dense(low_g, "low_g")
+    assert conv_w.shape == (C, taps) and qkv.shape == (T, C) and beta.shape == (T, n_heads)
+    assert low_a.shape == (T, decay_rank) and low_g.shape == (T, gate_rank)
+    dt = low_a.dtype
+    assert low_g.dtype == dt and (row is None or row.dtype == dt)
+    sp, ss = _state_args(state)
+    with _span("delta_prepare", _nbytes(row, partial, qkv, beta, low_a, low_g)):
+        _check(library().agv_delta_prepare(
+            rp, ctypes.c_longlong(ld), pp, ns, dtype_code(dt), T, ctx.batch, n_qk_heads, n_heads,
+            head_dim, value_dim, taps, decay_rank, gate_rank, _ptr(conv_w),
+            ctypes.c_float(unit_eps), ctypes.c_float(q_mult), sp, ss, ctypes.c_longlong(conv_off),
+            _ptr(ctx.slots), _ptr(ctx.cu_seqlens), _ptr(ctx.seq_index), _ptr(ctx.positions),
+            0 if ctx.mode == "decode" else 1, _ptr(qkv), _ptr(beta), _ptr(low_a), _ptr(low_g),
+            _stream()))
+
+
+def delta_scan(qkv: torch.Tensor, beta: torch.Tensor, a: torch.Tensor, dt_bias: torch.Tensor,
+               neg_a: torch.Tensor, out: torch.Tensor, ctx, state: torch.Tensor,
+               n_qk_heads: int, n_heads: int, head_dim: int, value_dim: int) -> None:
+    """The recurrence  S <- diag(g) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q  over the
+    step's tokens, sequence by sequence, with g = exp(neg_a[h] * softplus(a + dt_bias)); S
+    [H, dv, d] of each sequence is read from and written to ``state``.  All 32-bit."""
+    T = qkv.shape[0]
+    for t, n in ((qkv, "qkv"), (beta, "beta"), (a, "a"), (dt_bias, "dt_bias"), (neg_a, "neg_a"),
+                 (out, "out")):
+        _f32(t, n); _dense(t, n)
+    assert a.shape == (T, n_heads * head_dim) and out.shape == (T, n_heads * value_dim)
+    assert dt_bias.numel() == n_heads * head_dim and neg_a.numel() == n_heads
+    sp, ss = _state_args(state)
+    flops = 6 * T * n_heads * head_dim * value_dim
+    with _span("delta_scan", _nbytes(qkv, beta, a, out), flops):
+        _check(library().agv_delta_scan(_ptr(qkv), _ptr(beta), _ptr(a), _ptr(dt_bias), _ptr(neg_a),
+                                        _ptr(out), T, ctx.batch, n_qk_heads, n_heads, head_dim,
+                                        value_dim, sp, ss, _ptr(ctx.slots), _ptr(ctx.cu_seqlens),
+                                        _stream()))
+
+
+def delta_out(o: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, eps: float, n_heads: int,
+              value_dim: int, ctx, y: torch.Tensor) -> None:
+    """y[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * w * sigmoid(gate[t, h, :]); o and gate are
+    32-bit [T, H * dv], y is in the compute dtype."""
+    T = o.shape[0]
+    _f32(o, "o"); _f32(gate, "gate"); _f32(w, "w"); _dense(o, "o"); _dense(gate, "gate")
+    _dense(y, "y")
+    assert o.shape == gate.shape == y.shape == (T, n_heads * value_dim) and w.numel() == value_dim
+    with _span("delta_out", _nbytes(o, gate, y)):
+        _check(library().agv_delta_out(_ptr(o), _ptr(gate), _ptr(w), ctypes.c_float(eps), T,
+                                       n_heads, value_dim, _ptr(ctx.seq_index), _ptr(ctx.slots),
+                                       _ptr(y), dtype_code(y.dtype), _stream()))
 
 
 # ------------------------------------------------------------------- sampling
@@ -1200,6 +1308,7 @@ def _attention_cost(ctx, q, k, v, out, n_heads, head_dim, window, n_kv_heads=0):
     lens = getattr(ctx, "lens_host", None)
     if lens is None:
         return _nbytes(q, k, v, out), 0
+    window = abs(window)          # (a mask of blocks is counted as a window of its size)
     seen = 0                      # (query, key) pairs
     kv_rows = 0                   # cache rows a decode step reads
     for n in lens:
@@ -1330,7 +1439,7 @@ def attention_decode_fused(partial: torch.Tensor, wq: Optional[torch.Tensor],
     if cos is not None:
         _dense(cos, "cos"); _dense(sin, "sin")
         assert cos.shape == (B, head_dim // 2) and sin.shape == cos.shape
-    max_keys = max(1, min(window, ctx.max_len) if window else ctx.max_len)
+    max_keys = max(1, min(abs(window), ctx.max_len) if window else ctx.max_len)
     _, n_splits = attention_decode_plan(head_dim, torch.bfloat16, max_keys)
     # the tensor-core form leaves at most one partial result per cluster, and at most 16
     # clusters share a sequence, however long the context may get
@@ -1362,7 +1471,7 @@ def attention_decode(q, out, view, ctx, n_heads, n_kv_heads, head_dim, scale, wi
     with _span(op, *_attention_cost(ctx, q, None, None, out, n_heads, head_dim, window,
                                     n_kv_heads)):
         if head_dim % 16 == 0 and head_dim <= 512 and hdv == head_dim and not values_in_keys:
-            max_keys = min(window, ctx.max_len) if window else ctx.max_len
+            max_keys = min(abs(window), ctx.max_len) if window else ctx.max_len
             attention_decode_split(q, out, view.k_pool, view.v_pool, view.page_table, ctx.slots,
                                    ctx.positions, view.page, view.cap, n_heads, n_kv_heads,
                                    head_dim, scale, window, max(1, max_keys), sinks=sinks,

@@ -6,6 +6,8 @@ from .norm import Identity, LayerNorm, RMSNorm
 from .rope import RotaryEmbedding
 from .attention import AttentionMixer
 from .latent import LatentAttentionMixer
+from .delta import ChannelDeltaMixer
+from .position import LearnedPosition
 from .feedforward import DenseFeedForward, GatedFeedForward
 from .moe import RoutedFeedForward
 from .block import Block
@@ -16,5 +18,5 @@ __all__ = ["KVRequest", "ParamSpec", "StateRequest", "feed_forward_class", "mixe
            "register_block", "register_feed_forward", "register_mixer", "register_norm",
            "register_position", "register_stream_position", "RMSNorm", "LayerNorm",
            "RoutedFeedForward", "RotaryEmbedding", "Identity", "LatentAttentionMixer",
-           "DenseFeedForward",
+           "DenseFeedForward", "ChannelDeltaMixer", "LearnedPosition",
            "AttentionMixer", "GatedFeedForward", "Block", "GatedLinear", "Linear"]

@@ -29,7 +29,11 @@ and values of the cache entry the run order names); q and k normed over the whol
 projection instead of head by head (``qk_norm_whole``), a sink of constant logit
 (``fixed_sink``), and a learned bias by distance added to the scaled scores
 (``distance_bias``; tensor ``distance_bias`` [rows, heads], expanded at load time into one
-row per distance).
+row per distance); a bias that falls linearly with distance at a slope per head
+(``distance_slope``: the same table, filled from the slopes); a mask of blocks counted from
+position 0 instead of a sliding window (``chunk``: the kernels take it as a negative window,
+the cache as a ring that holds one block); values mixed with an earlier layer's of the same
+token before they are cached (``value_mix``; tensor ``value_mix``, a scalar).
 """
 from __future__ import annotations
 
@@ -68,6 +72,19 @@ class AttentionMixer:
         self.dist_bias: Optional[torch.Tensor] = None
         fixed = getattr(spec, "fixed_sink", None)
         self.fixed_sink = None if fixed is None else float(fixed)
+        self.slope_spec = getattr(spec, "distance_slope", None)
+        self.chunk = getattr(spec, "chunk", None)
+        self.value_mix = getattr(spec, "value_mix", None)
+        self.mix_weight = 0.0
+        if self.chunk is not None and (self.chunk < 1 or spec.window is not None):
+            raise ValueError("a mask of blocks needs a positive size and goes without a window")
+        if self.slope_spec is not None and (self.dist_spec is not None or
+                                            self.slope_spec.reach < 1):
+            raise ValueError("a bias by distance is either a learned table or a slope per head, "
+                             "and a slope needs the greatest distance a query can see")
+        if self.value_mix is not None and not self.whole_norm:
+            raise ValueError("mixed values go with the norm over the whole projection (its "
+                             "kernel mixes them)")
         if self.whole_norm and (spec.qk_norm is None or self.position is not None or
                                 self.q_temp is not None or not self.own_kv):
             raise ValueError("a norm over the whole projection needs qk_norm and goes without a "
@@ -79,7 +96,9 @@ class AttentionMixer:
         # the options the standard kernels' callers do not pass
         self.plain = (self.own_kv and self.value_dim == spec.head_dim and self.q_temp is None
                       and not getattr(spec, "sink", False) and not self.whole_norm
-                      and self.dist_spec is None and self.fixed_sink is None)
+                      and self.dist_spec is None and self.fixed_sink is None
+                      and self.slope_spec is None and self.chunk is None
+                      and self.value_mix is None)
 
     @classmethod
     def param_specs(cls, spec: AttentionSpec, hidden_size: int) -> Dict[str, ParamSpec]:
@@ -104,6 +123,8 @@ class AttentionMixer:
         db = getattr(spec, "distance_bias", None)
         if db is not None:
             p["distance_bias"] = ParamSpec((db.rows, spec.n_heads), "float32")
+        if getattr(spec, "value_mix", None) is not None:
+            p["value_mix"] = ParamSpec((), "float32")
         return p
 
     @staticmethod
@@ -123,7 +144,9 @@ class AttentionMixer:
     def cache_request(self):
         if not self.own_kv:
             return None
-        return KVRequest(self.spec.n_kv_heads, self.spec.head_dim, self.spec.window,
+        # (a mask of blocks needs the keys of one block: a ring of that many rows)
+        return KVRequest(self.spec.n_kv_heads, self.spec.head_dim,
+                         self.chunk if self.chunk is not None else self.spec.window,
                          0 if self.value_dim == self.spec.head_dim else self.value_dim)
 
     def load(self, tensors: Dict[str, torch.Tensor], dtype: torch.dtype,
@@ -161,6 +184,18 @@ class AttentionMixer:
             idx = torch.tensor(self.distance_rows(db.rows, db.far, max(n, 1)), device=device)
             table = tensors["distance_bias"].to(device=device, dtype=torch.float32)
             self.dist_bias = table[idx].t().contiguous()          # [heads, distances]
+        if self.slope_spec is not None:
+            # the same table from the slopes: entry [a, n] = -slope_a * n, made in 64-bit
+            sl = self.slope_spec
+            n = int(sl.reach) if self.chunk is None else min(int(sl.reach), int(self.chunk))
+            heads = torch.arange(1, self.spec.n_heads + 1, dtype=torch.float64)
+            slopes = torch.pow(torch.tensor(2.0, dtype=torch.float64),
+                               -float(sl.exponent) * heads / self.spec.n_heads)
+            dist = torch.arange(max(n, 1), dtype=torch.float64)
+            self.dist_bias = (-(slopes[:, None] * dist[None, :])).to(
+                device=device, dtype=torch.float32).contiguous()
+        if self.value_mix is not None and self.value_mix.source is not None:
+            self.mix_weight = float(tensors["value_mix"].to(torch.float32).reshape(()).item())
 
     def forward(self, x: torch.Tensor, ctx, cache_entry: int, writes_cache: bool) -> torch.Tensor:
         if not self.plain:
@@ -244,9 +279,11 @@ class AttentionMixer:
         view = ctx.cache.kv_view(cache_entry)
         eps = s.qk_norm.eps if s.qk_norm is not None else 0.0
         window = s.window or 0
-        if window >= ctx.cache.max_seq_len:
-            # a window no sequence of this cache can outgrow is no window (its group keeps
-            # every key, in rows that may be fewer than the window)
+        if self.chunk is not None:
+            window = -int(self.chunk)
+        if abs(window) >= ctx.cache.max_seq_len:
+            # a window (or block) no sequence of this cache can outgrow is none (its group
+            # keeps every key, in rows that may be fewer than the window)
             window = 0
         n_own = nkv if self.own_kv else 0
         width = (nh + n_own) * hd + n_own * hdv
@@ -264,9 +301,15 @@ class AttentionMixer:
         qkv = proj if part is None else ctx.new(T, width)
         vt = None
         if self.whole_norm:
+            v_first = None
+            if self.value_mix is not None and self.value_mix.source is not None:
+                v_first = ctx.step_values[self.value_mix.source]
             kernels.proj_norm_store(qkv, nh * hd, nkv * hd, nkv * hdv, self.q_norm_weight,
                                     self.k_norm_weight, eps, ctx.positions, view, ctx,
-                                    partial=part)
+                                    partial=part, v_first=v_first, v_mix=self.mix_weight)
+            if self.value_mix is not None and self.value_mix.source is None:
+                # the values as projected, for the layers that lean on them
+                ctx.step_values[cache_entry] = qkv[:, (nh + nkv) * hd:]
         elif self.own_kv:
             if ctx.mode == PREFILL and kernels.attention_prefill_wants_transposed_values(
                     qkv, hd, hdv):

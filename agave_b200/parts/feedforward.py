@@ -52,11 +52,12 @@ register_feed_forward("gated_dense", GatedFeedForward)
 
 
 class DenseFeedForward:
-    """down(act(up x)): no gate.  "relu2" is the squared relu, max(z, 0)^2."""
+    """down(act(up x)): no gate.  "relu2" is the squared relu, max(z, 0)^2; "gelu_erf" is
+    z / 2 * (1 + erf(z / sqrt 2))."""
 
     def __init__(self, spec: DenseFeedForwardSpec, hidden_size: int, dtype: torch.dtype,
                  device: torch.device):
-        if spec.activation != "relu2":
+        if spec.activation not in ("relu2", "gelu_erf"):
             raise ValueError(f"dense feed-forward: unknown activation {spec.activation!r}")
         self.spec, self.hidden_size = spec, hidden_size
         self.up: Optional[Linear] = None

@@ -32,7 +32,7 @@ class Linear:
         return out
 
     def activated(self, x: torch.Tensor, activation: str) -> torch.Tensor:
-        """act(x w^T) in x's dtype ("relu2": the squared relu)."""
+        """act(x w^T) in x's dtype ("relu2": the squared relu; "gelu_erf": the erf GELU)."""
         out = torch.empty((x.shape[0], self.out_features), dtype=x.dtype, device=x.device)
         kernels.linear_activated(x, self.weight, out, activation, op=self.role)
         return out

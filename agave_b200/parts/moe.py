@@ -17,6 +17,12 @@ follows adds the choices in order, as it adds the ranges of K of a dense project
 
 The experts' matrices are stacked [E, ...] at load time so that a tile finds its expert
 by index.
+
+Options of the spec: a bias on the router's logits (``router_bias``); weights that are the
+softmax over the chosen experts' logits, the logits making the choice (``weighting``
+"softmax_top"); and a shared expert of the same form that every token uses, its output
+multiplied by sigmoid(w_sg . x), one number per token (``shared_size``): it is one more
+slice of the partial sums.
 """
 from __future__ import annotations
 
@@ -27,6 +33,7 @@ import torch
 from .. import kernels
 from ..config.base import RoutedFeedForwardSpec
 from .base import ParamSpec, register_feed_forward
+from .linear import GatedLinear, Linear
 
 
 class RoutedFeedForward:
@@ -39,6 +46,15 @@ class RoutedFeedForward:
         if spec.top > spec.keep_groups * (spec.n_experts // spec.n_groups):
             raise ValueError("top exceeds the experts of the groups kept")
         self.spec, self.hidden_size, self.dtype = spec, hidden_size, dtype
+        self.weighting = getattr(spec, "weighting", "sigmoid")
+        if self.weighting not in ("sigmoid", "softmax_top"):
+            raise ValueError(f"unknown expert weighting {self.weighting!r}")
+        if self.weighting == "softmax_top" and spec.correction:
+            raise ValueError("weights by softmax over the chosen logits go without a correction")
+        self.has_bias = bool(getattr(spec, "router_bias", False))
+        self.shared_size = int(getattr(spec, "shared_size", 0) or 0)
+        self.router_bias: Optional[torch.Tensor] = None
+        self.shared_gate_up = self.shared_down = self.shared_gate = None
         self.w_router: Optional[torch.Tensor] = None
         self.correction: Optional[torch.Tensor] = None
         self.w_gate = self.w_up = self.w_down = None
@@ -53,6 +69,14 @@ class RoutedFeedForward:
             p[f"experts.{e}.gate_proj.weight"] = ParamSpec((ff, hidden_size))
             p[f"experts.{e}.up_proj.weight"] = ParamSpec((ff, hidden_size))
             p[f"experts.{e}.down_proj.weight"] = ParamSpec((hidden_size, ff))
+        if getattr(spec, "router_bias", False):
+            p["router.bias"] = ParamSpec((spec.n_experts,), "float32")
+        sf = int(getattr(spec, "shared_size", 0) or 0)
+        if sf:
+            p["shared.gate_proj.weight"] = ParamSpec((sf, hidden_size))
+            p["shared.up_proj.weight"] = ParamSpec((sf, hidden_size))
+            p["shared.down_proj.weight"] = ParamSpec((hidden_size, sf))
+            p["shared.gate.weight"] = ParamSpec((1, hidden_size))
         return p
 
     def load(self, tensors: Dict[str, torch.Tensor], dtype: torch.dtype,
@@ -65,6 +89,17 @@ class RoutedFeedForward:
             self.correction = tensors["router.correction"].to(
                 device=device, dtype=torch.float32).contiguous()
         self.w_gate, self.w_up, self.w_down = stack("gate_proj"), stack("up_proj"), stack("down_proj")
+        if self.has_bias:
+            self.router_bias = tensors["router.bias"].to(device=device,
+                                                         dtype=torch.float32).contiguous()
+        if self.shared_size:
+            def mat(name):
+                return tensors[name].to(device=device, dtype=dtype).contiguous()
+            self.shared_gate_up = GatedLinear(mat("shared.gate_proj.weight"),
+                                              mat("shared.up_proj.weight"), self.spec.activation,
+                                              role="shared_gate_up")
+            self.shared_down = Linear(mat("shared.down_proj.weight"), role="shared_down")
+            self.shared_gate = mat("shared.gate.weight").reshape(-1).contiguous()
 
     def route(self, x: torch.Tensor):
         """(ids [T, top] int32, weights [T, top] 32-bit) of the tokens of x."""
@@ -73,8 +108,14 @@ class RoutedFeedForward:
         ids = torch.empty((T, s.top), dtype=torch.int32, device=x.device)
         wts = torch.empty((T, s.top), dtype=torch.float32, device=x.device)
         kernels.moe_route(x, self.w_router, self.correction, s.n_groups, s.keep_groups, s.top,
-                          ids, wts)
+                          ids, wts, bias=self.router_bias,
+                          softmax_top=self.weighting == "softmax_top")
         return ids, wts
+
+    def _shared(self, x: torch.Tensor, out: torch.Tensor) -> None:
+        """out [T, H] (32-bit) = sigmoid(w_sg . x) * down(act(gate x) * up x)."""
+        self.shared_down(self.shared_gate_up(x), out=out)
+        kernels.row_gate(x, self.shared_gate, out)
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         s = self.spec
@@ -82,7 +123,10 @@ class RoutedFeedForward:
         ids, wts = self.route(x)
         plan = kernels.moe_plan(ids, wts, s.n_experts)
         z = torch.empty((plan.rows, s.intermediate_size), dtype=x.dtype, device=x.device)
-        y = torch.empty((s.top, T, H), dtype=torch.float32, device=x.device)
+        n_sh = 1 if self.shared_size else 0
+        y = torch.empty((s.top + n_sh, T, H), dtype=torch.float32, device=x.device)
+        if n_sh:
+            self._shared(x, y[s.top])
         if (kernels.moe_grouped_tc_supported(x, self.w_gate) and
                 kernels.moe_grouped_tc_supported(z, self.w_down)):
             # bfloat16 on the tensor cores: the tokens are brought into the plan's order
@@ -91,12 +135,12 @@ class RoutedFeedForward:
             kernels.moe_gather_rows(x, plan, xs)
             kernels.moe_grouped_tc(xs, self.w_gate, z, plan, w2=self.w_up,
                                    activation=s.activation, op="experts_gate_up")
-            kernels.moe_grouped_tc(z, self.w_down, y.view(s.top * T, H), plan, scatter=True,
+            kernels.moe_grouped_tc(z, self.w_down, y[:s.top].view(s.top * T, H), plan, scatter=True,
                                    op="experts_down")
             return y
         kernels.moe_grouped(x, self.w_gate, z, plan, w2=self.w_up, activation=s.activation,
                             gather=True, op="experts_gate_up")
-        kernels.moe_grouped(z, self.w_down, y.view(s.top * T, H), plan, scatter=True,
+        kernels.moe_grouped(z, self.w_down, y[:s.top].view(s.top * T, H), plan, scatter=True,
                             op="experts_down")
         return y
 
