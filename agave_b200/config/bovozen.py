@@ -157,8 +157,12 @@ class BovozenConfig:
         eos_ids = () if eos is None else tuple(int(e) for e in eos) if isinstance(eos, list) \
             else (int(eos),)
         bos = raw.get("bos_token_id")
+        if raw.get("max_positions") is None and shapes is not None and shapes("pos") is not None:
+            positions = int(shapes("pos")[0])          # as many as the table has rows
+        else:
+            positions = _get(raw, "max_positions", "")
         cfg = cls(vocab=_get(raw, "vocab", ""), width=_get(raw, "width", ""),
-                  max_positions=_get(raw, "max_positions", ""),
+                  max_positions=positions,
                   norm_eps=_get(_get(raw, "norm", "", typ=None), "eps", "norm.", float),
                   layers=tuple(layers), bos_token_id=None if bos is None else int(bos),
                   eos_token_ids=eos_ids)
