@@ -42,6 +42,9 @@ _EXPERT = re.compile(r"^experts\.(\d+)\.(gate|up|down)_proj\.weight$")
 @dataclass(frozen=True)
 class BovozenWeightNames:
     prefixes: Tuple[str, ...] = ("",)
+    # names a checkpoint may carry although the model does not use them: the mixing scalar
+    # of an attention layer that mixes nothing
+    ignore_prefixes: Tuple[str, ...] = ()
 
     def checkpoint_name(self, internal: str, prefix: str) -> str:
         if internal == "embed.weight":
@@ -68,7 +71,9 @@ class BovozenWeightNames:
 
 
 def _weight_names(config: BovozenConfig) -> BovozenWeightNames:
-    return BovozenWeightNames()
+    unused = tuple(f"l{i}.mix.vmix" for i, layer in enumerate(config.layers)
+                   if layer.mixer.kind == "attention" and not layer.mixer.v_mix)
+    return BovozenWeightNames(ignore_prefixes=unused)
 
 
 register_architecture("Bovozen", BovozenConfig, _weight_names, model_types=("bovozen",))

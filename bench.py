@@ -35,7 +35,9 @@ and every operation's device time with its share of the measured peaks
 Zazerax decoder (layers alternating latent attention of both kinds with windowed attention,
 dense squared-relu feed-forward) beside a Gemma 3 decoder of equal width, heads, layers and
 vocabulary whose every second layer has the same window and whose gated feed-forward has as
-many weights.
+many weights.  ``--compare bovozen`` sets the Bovozen decoder (attention over blocks of positions
+alternating with the gated delta rule, routed experts beside a gated shared one) beside the
+Ramilorn decoder of equal width, heads, experts, layers and vocabulary.
 """
 import argparse
 import json
@@ -297,6 +299,31 @@ def compare_configs_zazerax(size):
     return zazerax, gemma
 
 
+def compare_configs_bovozen(size):
+    """Bovozen beside Ramilorn, the library's other decoder with routed experts: equal width,
+    heads, head size, experts, layers and vocabulary.  Bovozen's layers alternate attention
+    over blocks of 1,024 positions (values leaning towards the first layer's) with the gated
+    delta rule (as many heads, state head size x head size per head, four taps); its experts
+    have a shared one of twice their width beside them."""
+    H, A, G, d, E, top, ff, groups, keep, L, V = COMPARE_SIZES[size]
+    att = {"dim": d, "heads": A, "kv_heads": G, "mask": {"size": 1024}, "scale": d ** -0.5,
+           "v_mix": True, "vdim": d}
+    rec = {"conv": 4, "dim": d, "heads": A, "kv_heads": G, "vdim": d, "decay_rank": 64,
+           "gate_rank": 64}
+    mlp = {"expert": {"ff": ff}, "kind": "moe", "router": {"experts": E, "top": top},
+           "shared": {"ff": 2 * ff}}
+    layers = [{"mixer": rec if l % 2 else att, "mlp": mlp,
+               "type": "channel_delta" if l % 2 else "attention"} for l in range(L)]
+    bovozen = {"architecture": "Bovozen", "layers": layers, "max_positions": 4096,
+               "norm": {"eps": 1e-6}, "vocab": V, "width": H}
+    return bovozen, compare_configs(size)[0]
+
+
+COMPARE_BUILDERS = {"ramilorn": (compare_configs, "gemma3"),
+                    "zazerax": (compare_configs_zazerax, "gemma3"),
+                    "bovozen": (compare_configs_bovozen, "ramilorn")}
+
+
 def run_compare(args):
     import torch
     from agave_b200 import kernels
@@ -307,13 +334,13 @@ def run_compare(args):
     from agave_b200.weights import random_tensors
     pk = peaks()
     batch, ctx_len, n_pre = 8, 1024, args.prefill_tokens
-    builder = compare_configs_zazerax if args.compare == "zazerax" else compare_configs
-    out = {"compare": f"{args.compare} beside gemma3 at equal size", "dtype": "bf16",
+    builder, beside = COMPARE_BUILDERS[args.compare]
+    out = {"compare": f"{args.compare} beside {beside} at equal size", "dtype": "bf16",
            "data": "synthetic", "decode_batch": batch, "decode_context": ctx_len,
            "prefill_tokens": n_pre, "peaks": pk, "sizes": {}}
     for size in (args.compare_sizes or sorted(COMPARE_SIZES)):
         entry = {}
-        for name, cfg in zip((args.compare, "gemma3"), builder(size)):
+        for name, cfg in zip((args.compare, beside), builder(size)):
             arch = resolve_architecture(cfg)
             specs = decoder_param_specs(arch.config_class.from_dict(cfg).to_model_spec())
             tensors = random_tensors(specs, 11, 0.02, 0.1, torch.bfloat16, "cuda:0")
@@ -429,9 +456,9 @@ def main():
                          "schedule's, 128 to 2,048 for the benchmark configuration)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
                     help="length of the timed prompt (default: the benchmark configuration's)")
-    ap.add_argument("--compare", default=None, choices=["ramilorn", "zazerax"],
-                    help="instead of the benchmark: this architecture beside Gemma 3 at equal "
-                         "layer sizes (see the module text)")
+    ap.add_argument("--compare", default=None, choices=sorted(COMPARE_BUILDERS),
+                    help="instead of the benchmark: this architecture beside the closest other "
+                         "one at equal layer sizes (see the module text)")
     ap.add_argument("--compare-sizes", nargs="+", default=None, choices=sorted(COMPARE_SIZES),
                     help="the sizes --compare runs (default: all)")
     args = ap.parse_args()
