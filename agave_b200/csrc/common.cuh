@@ -74,6 +74,20 @@ inline void agv_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t sme
     (void)cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);   // error: cudaGetLastError
 }
 
+// A launch that starts only when the kernel before it has finished: for a kernel whose speed
+// rests on its CTAs being spread evenly over the SMs (few CTAs, each a long dependent chain).
+// Let in early, its CTAs would settle on whichever SMs the kernel before frees first.
+template <typename... KArgs, typename... Args>
+inline void agv_launch_after(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                             cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    (void)cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);   // error: cudaGetLastError
+}
+
 // The same with the CTAs grouped into thread-block clusters.
 template <typename... KArgs, typename... Args>
 inline void agv_launch_cluster(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,

@@ -59,8 +59,14 @@ __device__ __forceinline__ float softplus_f(float t) {
 }
 
 // ------------------------------------------------------------------ prepare
-// One CTA per token.  fused_state: the CTA's token is the only one its sequence brings (a
-// decode step), so it also shifts the convolution's inputs by one.
+// The convolution's inputs of a sequence are a ring by position: the input of position pp is
+// row pp % (taps - 1) of the slot's [taps - 1, C] block, so a step writes the rows of its own
+// last taps - 1 positions and moves nothing.
+//
+// One CTA per token.  The token's row of the stacked product comes into shared memory first
+// (all its loads in flight at once), earlier tokens of the same step are read in place.
+// fused_state: the CTA's token is the only one its sequence brings (a decode step), so it
+// also stores its inputs in the ring.
 template <typename T>
 __global__ void __launch_bounds__(256)
 delta_prepare_kernel(RowIn<T> in, DeltaDims dm, DeltaState st, const float* __restrict__ conv_w,
@@ -73,27 +79,33 @@ delta_prepare_kernel(RowIn<T> in, DeltaDims dm, DeltaState st, const float* __re
     const int b = st.seq_index[t];
     const int slot = st.slots[b];
     if (slot < 0) return;
-    const int C = dm.C(), nq = dm.nq(), taps = dm.taps;
+    const int C = dm.C(), nq = dm.nq(), taps = dm.taps, R = taps - 1;
+    float* rowbuf = buf + C;                     // [W] the token's row, 32-bit
     const int p = st.positions[t];
     const int first = st.cu[b];                  // first token of the sequence in this step
     const int p0 = p - (t - first);              // its position
-    float* cs = st.state + (size_t)slot * st.stride + st.conv_off;
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
-        const float* w = conv_w + (size_t)c * taps;
-        float acc = 0.f;
-        // oldest input first; input p - k meets weight taps - 1 - k
-        for (int k = taps - 1; k >= 0; --k) {
-            const int pp = p - k;
-            float x = 0.f;
-            if (pp >= p0) x = in.at(t - k, c);
-            else if (pp >= 0) x = cs[(size_t)(pp - p0 + taps - 1) * C + c];
-            acc = fmaf(w[taps - 1 - k], x, acc);
+    in.load(t, rowbuf);
+    {
+        const float* __restrict__ cs = st.state + (size_t)slot * st.stride + st.conv_off;
+#pragma unroll 4
+        for (int c = threadIdx.x; c < C; c += blockDim.x) {
+            const float* w = conv_w + (size_t)c * taps;
+            float acc = 0.f;
+            // oldest input first; input p - k meets weight taps - 1 - k
+            for (int k = R; k >= 1; --k) {
+                const int pp = p - k;
+                float x = 0.f;
+                if (pp >= p0) x = in.at(t - k, c);
+                else if (pp >= 0) x = cs[(size_t)(pp % R) * C + c];
+                acc = fmaf(w[R - k], x, acc);
+            }
+            buf[c] = silu_f(fmaf(w[R], rowbuf[c], acc));
         }
-        buf[c] = silu_f(acc);
-        if (fused_state && taps > 1) {
-            for (int i = 0; i + 2 < taps; ++i) cs[(size_t)i * C + c] = cs[(size_t)(i + 1) * C + c];
-            cs[(size_t)(taps - 2) * C + c] = in.at(t, c);
-        }
+    }
+    if (fused_state && R > 0) {
+        // (the row of position p is the one position p - R had: read above by this thread)
+        float* cs = st.state + (size_t)slot * st.stride + st.conv_off + (size_t)(p % R) * C;
+        for (int c = threadIdx.x; c < C; c += blockDim.x) cs[c] = rowbuf[c];
     }
     __syncthreads();
     // unit vectors: q heads, then k heads (2 G groups of d), a warp a group
@@ -109,15 +121,16 @@ delta_prepare_kernel(RowIn<T> in, DeltaDims dm, DeltaState st, const float* __re
     }
     for (int c = 2 * nq + threadIdx.x; c < C; c += blockDim.x) orow[c] = buf[c];
     for (int h = threadIdx.x; h < dm.H; h += blockDim.x)
-        beta[(size_t)t * dm.H + h] = sigmoid_f(in.at(t, C + h));
+        beta[(size_t)t * dm.H + h] = sigmoid_f(rowbuf[C + h]);
     for (int i = threadIdx.x; i < dm.ra; i += blockDim.x)
-        low_a[(size_t)t * dm.ra + i] = from_f32<T>(in.at(t, C + dm.H + i));
+        low_a[(size_t)t * dm.ra + i] = from_f32<T>(rowbuf[C + dm.H + i]);
     for (int i = threadIdx.x; i < dm.rg; i += blockDim.x)
-        low_g[(size_t)t * dm.rg + i] = from_f32<T>(in.at(t, C + dm.H + dm.ra + i));
+        low_g[(size_t)t * dm.rg + i] = from_f32<T>(rowbuf[C + dm.H + dm.ra + i]);
 }
 
-// The convolution's inputs after a step of several tokens a sequence: the last taps - 1 of
-// what the sequence has seen.  One CTA per sequence, a thread a channel; it runs after the
+// The convolution's inputs after a step of several tokens a sequence: the step's last
+// taps - 1 positions go to their rows of the ring (fewer, if the step is shorter: the rows of
+// earlier positions stay).  One CTA per sequence, a thread a channel; it runs after the
 // prepare kernel, which reads the inputs of before the step.
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -127,20 +140,15 @@ delta_conv_state_kernel(RowIn<T> in, DeltaDims dm, DeltaState st) {
     const int b = blockIdx.x;
     const int slot = st.slots[b];
     if (slot < 0) return;
-    const int C = dm.C(), taps = dm.taps;
+    const int C = dm.C(), R = dm.taps - 1;
     const int first = st.cu[b], n = st.cu[b + 1] - first;
-    if (n <= 0) return;
+    if (n <= 0 || R <= 0) return;
     const int p0 = st.positions[first], len = p0 + n;
+    const int from = len - R > p0 ? len - R : p0;
     float* cs = st.state + (size_t)slot * st.stride + st.conv_off;
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
-        for (int i = 0; i + 1 < taps; ++i) {
-            const int pp = len - (taps - 1) + i;
-            float x = 0.f;
-            if (pp >= p0) x = in.at(first + pp - p0, c);
-            else if (pp >= 0) x = cs[(size_t)(pp - p0 + taps - 1) * C + c];   // an entry after i
-            cs[(size_t)i * C + c] = x;
-        }
-    }
+    for (int c = threadIdx.x; c < C; c += blockDim.x)
+        for (int pp = from; pp < len; ++pp)
+            cs[(size_t)(pp % R) * C + c] = in.at(first + pp - p0, c);
 }
 
 // --------------------------------------------------------------------- scan
@@ -148,7 +156,7 @@ delta_conv_state_kernel(RowIn<T> in, DeltaDims dm, DeltaState st) {
 // column (L a power of two, L * 16 >= d), thread = column * L + lane.  The tokens of the
 // sequence come through shared memory TCH at a time: k, q and the decay of the head's key
 // channels (padded with zeros to L * 16 rows, which keeps the padded rows of S at zero), the
-// CTA's columns of v, and beta.
+// CTA's columns of v, and beta.  L is a template parameter: the shuffle rounds are unrolled.
 struct ScanArgs {
     const float* qkv;          // [T, C]: q | k | v, prepared
     const float* beta;         // [T, H]
@@ -159,10 +167,48 @@ struct ScanArgs {
     int L, CC, TCH;
 };
 
+// A 4-byte asynchronous copy into shared memory (the sources are rows of 32-bit tensors at
+// offsets that need not be multiples of 16 bytes).
+__device__ __forceinline__ void cp_async_f32(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;"
+                 :: "r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" :: "n"(N) : "memory"); }
+
+// The tokens come through two buffers: while the lanes run the recurrence over one, the next
+// TCH tokens' k, q, decay pre-activation, v and beta are on their way (asynchronous copies),
+// so the trip to L2 or HBM is paid once a sequence, not once a buffer.  When a buffer has
+// arrived, what does not depend on the state is made in place: the decay g (bias, softplus,
+// exp), g * k, g * q and the token's k . q.  With them a token is one round of dot products,
+//
+//      a = (g S)^T k = sum_r S_r (g k)_r      r = (g S)^T q = sum_r S_r (g q)_r
+//      u = beta (v - a);    o = r + (k . q) u;    S <- g S + k u
+//
+// the same sums as  S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q  with the
+// read-out split into the part the state had and the token's own write: one round of
+// shuffles a token instead of two, and the state's update off the output's path.
+struct ScanBuf {
+    float *k, *gk, *gq, *g, *v, *beta, *kq;
+    __device__ ScanBuf(float* base, int TCH, int Dp, int CC) {
+        k = base;
+        gk = k + (size_t)TCH * Dp;       // (q arrives in gq's place, the pre-activation in g's)
+        gq = gk + (size_t)TCH * Dp;
+        g = gq + (size_t)TCH * Dp;
+        v = g + (size_t)TCH * Dp;
+        beta = v + (size_t)TCH * CC;
+        kq = beta + TCH;
+    }
+};
+__host__ __device__ inline size_t scan_buf_floats(int TCH, int Dp, int CC) {
+    return ((size_t)TCH * (4 * Dp + CC + 2) + 3) / 4 * 4;      // (16-byte rows in the next buffer)
+}
+
+template <int L>
 __global__ void __launch_bounds__(256)
 delta_scan_kernel(ScanArgs a, DeltaDims dm, DeltaState st) {
     pdl_wait();
-    pdl_launch_next();
     extern __shared__ float smem[];
     const int b = blockIdx.z;
     const int slot = st.slots[b];
@@ -171,86 +217,130 @@ delta_scan_kernel(ScanArgs a, DeltaDims dm, DeltaState st) {
     if (n <= 0) return;
     const int h = blockIdx.y, g = h / (dm.H / dm.G);
     const int d = dm.d, dv = dm.dv, C = dm.C(), nq = dm.nq();
-    const int L = a.L, CC = a.CC, TCH = a.TCH, Dp = L * DL_R;
+    constexpr int Dp = L * DL_R;
+    const int CC = a.CC, TCH = a.TCH;
     const int l = threadIdx.x & (L - 1);
     const int jc = threadIdx.x / L;
     const int j = blockIdx.x * CC + jc;
     const bool live = jc < CC && j < dv;
-    float* sk = smem;                          // [TCH][Dp]
-    float* sq = sk + (size_t)TCH * Dp;
-    float* sg = sq + (size_t)TCH * Dp;
-    float* sv = sg + (size_t)TCH * Dp;         // [TCH][CC]
-    float* sb = sv + (size_t)TCH * CC;         // [TCH]
+    const size_t per = scan_buf_floats(TCH, Dp, CC);
+    float* sdt = smem + 2 * per;                                   // the decay's bias [Dp]
+    for (size_t i = threadIdx.x; i < 2 * per; i += blockDim.x) smem[i] = 0.f;   // the padding stays 0
+    for (int r = threadIdx.x; r < Dp; r += blockDim.x)
+        sdt[r] = r < d ? a.dt_bias[(size_t)h * d + r] : 0.f;
+    __syncthreads();
+
+    auto fetch = [&](int c0, float* base) {
+        const int m = min(TCH, n - c0);
+        const ScanBuf sb(base, TCH, Dp, CC);
+        for (int idx = threadIdx.x; idx < m * Dp; idx += blockDim.x) {
+            const int tt = idx / Dp, r = idx - tt * Dp;
+            if (r < d) {
+                const size_t t = (size_t)(t0 + c0 + tt);
+                cp_async_f32(sb.gq + idx, a.qkv + t * C + (size_t)g * d + r);          // q
+                cp_async_f32(sb.k + idx, a.qkv + t * C + nq + (size_t)g * d + r);
+                cp_async_f32(sb.g + idx, a.a + t * dm.H * d + (size_t)h * d + r);      // pre-activation
+            }
+        }
+        for (int idx = threadIdx.x; idx < m * CC; idx += blockDim.x) {
+            const int tt = idx / CC, c = idx - tt * CC;
+            const int col = blockIdx.x * CC + c;
+            if (col < dv)
+                cp_async_f32(sb.v + idx, a.qkv + (size_t)(t0 + c0 + tt) * C + 2 * nq + (size_t)h * dv + col);
+        }
+        for (int tt = threadIdx.x; tt < m; tt += blockDim.x)
+            cp_async_f32(sb.beta + tt, a.beta + (size_t)(t0 + c0 + tt) * dm.H + h);
+        cp_async_commit();
+    };
 
     float S[DL_R];
     float* srow = st.state + (size_t)slot * st.stride + ((size_t)h * dv + (live ? j : 0)) * d;
+    fetch(0, smem);
 #pragma unroll
     for (int i = 0; i < DL_R; ++i) {
         const int r = l * DL_R + i;
         S[i] = live && r < d ? srow[r] : 0.f;
     }
     const float na = a.neg_a[h];
-    for (int c0 = 0; c0 < n; c0 += TCH) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    int cur = 0;
+    for (int c0 = 0; c0 < n; c0 += TCH, cur ^= 1) {
         const int m = min(TCH, n - c0);
+        const ScanBuf sb(smem + (size_t)cur * per, TCH, Dp, CC);
+        // (the other buffer was read in the round before, which ended with a barrier)
+        if (c0 + TCH < n) {
+            fetch(c0 + TCH, smem + (size_t)(cur ^ 1) * per);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        // k . q of each token (a warp a token), before q becomes g * q
+        for (int tt = warp; tt < m; tt += nwarps) {
+            float s = 0.f;
+            for (int r = lane; r < Dp; r += 32) s = fmaf(sb.k[tt * Dp + r], sb.gq[tt * Dp + r], s);
+            s = warp_sum(s);
+            if (lane == 0) sb.kq[tt] = s;
+        }
         __syncthreads();
         for (int idx = threadIdx.x; idx < m * Dp; idx += blockDim.x) {
-            const int tt = idx / Dp, r = idx - tt * Dp;
-            const size_t t = (size_t)(t0 + c0 + tt);
-            float kv = 0.f, qv = 0.f, gv = 0.f;
+            const int r = idx % Dp;
             if (r < d) {
-                qv = a.qkv[t * C + (size_t)g * d + r];
-                kv = a.qkv[t * C + nq + (size_t)g * d + r];
-                const float pre = a.a[t * dm.H * d + (size_t)h * d + r] + a.dt_bias[(size_t)h * d + r];
-                gv = expf(na * softplus_f(pre));
+                const float gv = expf(na * softplus_f(sb.g[idx] + sdt[r]));
+                sb.g[idx] = gv;
+                sb.gk[idx] = gv * sb.k[idx];
+                sb.gq[idx] = gv * sb.gq[idx];
             }
-            sk[idx] = kv; sq[idx] = qv; sg[idx] = gv;
         }
-        for (int idx = threadIdx.x; idx < m * CC; idx += blockDim.x) {
-            const int tt = idx / CC, c = idx - tt * CC;
-            const int col = blockIdx.x * CC + c;
-            sv[idx] = col < dv ? a.qkv[(size_t)(t0 + c0 + tt) * C + 2 * nq + (size_t)h * dv + col] : 0.f;
-        }
-        for (int tt = threadIdx.x; tt < m; tt += blockDim.x)
-            sb[tt] = a.beta[(size_t)(t0 + c0 + tt) * dm.H + h];
         __syncthreads();
+        const float* pk = sb.k + l * DL_R;
+        const float* pgk = sb.gk + l * DL_R;
+        const float* pgq = sb.gq + l * DL_R;
+        const float* pg = sb.g + l * DL_R;
+        const float* pv = sb.v + (jc < CC ? jc : 0);
+        float* po = a.out + (size_t)(t0 + c0) * dm.H * dv + (size_t)h * dv + (live ? j : 0);
+#pragma unroll 2
         for (int tt = 0; tt < m; ++tt) {
-            const float4* k4 = reinterpret_cast<const float4*>(sk + (size_t)tt * Dp + l * DL_R);
-            const float4* q4 = reinterpret_cast<const float4*>(sq + (size_t)tt * Dp + l * DL_R);
-            const float4* g4 = reinterpret_cast<const float4*>(sg + (size_t)tt * Dp + l * DL_R);
-            float kk[DL_R];
-            float acc0 = 0.f, acc1 = 0.f;
+            float gk[DL_R], gq[DL_R], kk[DL_R], gg[DL_R];
 #pragma unroll
             for (int i = 0; i < DL_R / 4; ++i) {
-                const float4 kq = k4[i], gq = g4[i];
-                kk[4 * i] = kq.x; kk[4 * i + 1] = kq.y; kk[4 * i + 2] = kq.z; kk[4 * i + 3] = kq.w;
-                S[4 * i] *= gq.x; S[4 * i + 1] *= gq.y; S[4 * i + 2] *= gq.z; S[4 * i + 3] *= gq.w;
-                acc0 = fmaf(S[4 * i], kq.x, acc0);
-                acc1 = fmaf(S[4 * i + 1], kq.y, acc1);
-                acc0 = fmaf(S[4 * i + 2], kq.z, acc0);
-                acc1 = fmaf(S[4 * i + 3], kq.w, acc1);
+                const float4 x = reinterpret_cast<const float4*>(pgk)[i];
+                const float4 y = reinterpret_cast<const float4*>(pgq)[i];
+                gk[4 * i] = x.x; gk[4 * i + 1] = x.y; gk[4 * i + 2] = x.z; gk[4 * i + 3] = x.w;
+                gq[4 * i] = y.x; gq[4 * i + 1] = y.y; gq[4 * i + 2] = y.z; gq[4 * i + 3] = y.w;
             }
-            float acc = acc0 + acc1;
-            for (int o = 1; o < L; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            const float u = sb[tt] * (sv[(size_t)tt * CC + (jc < CC ? jc : 0)] - acc);
-            float o0 = 0.f, o1 = 0.f;
+            float ac[4] = {0.f, 0.f, 0.f, 0.f}, rc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int i = 0; i < DL_R; ++i) {
+                ac[i & 3] = fmaf(S[i], gk[i], ac[i & 3]);
+                rc[i & 3] = fmaf(S[i], gq[i], rc[i & 3]);
+            }
 #pragma unroll
             for (int i = 0; i < DL_R / 4; ++i) {
-                const float4 qq = q4[i];
-                S[4 * i] = fmaf(kk[4 * i], u, S[4 * i]);
-                S[4 * i + 1] = fmaf(kk[4 * i + 1], u, S[4 * i + 1]);
-                S[4 * i + 2] = fmaf(kk[4 * i + 2], u, S[4 * i + 2]);
-                S[4 * i + 3] = fmaf(kk[4 * i + 3], u, S[4 * i + 3]);
-                o0 = fmaf(S[4 * i], qq.x, o0);
-                o1 = fmaf(S[4 * i + 1], qq.y, o1);
-                o0 = fmaf(S[4 * i + 2], qq.z, o0);
-                o1 = fmaf(S[4 * i + 3], qq.w, o1);
+                const float4 x = reinterpret_cast<const float4*>(pk)[i];
+                const float4 y = reinterpret_cast<const float4*>(pg)[i];
+                kk[4 * i] = x.x; kk[4 * i + 1] = x.y; kk[4 * i + 2] = x.z; kk[4 * i + 3] = x.w;
+                gg[4 * i] = y.x; gg[4 * i + 1] = y.y; gg[4 * i + 2] = y.z; gg[4 * i + 3] = y.w;
             }
-            float ov = o0 + o1;
-            for (int o = 1; o < L; o <<= 1) ov += __shfl_xor_sync(0xffffffffu, ov, o);
-            if (live && l == 0)
-                a.out[(size_t)(t0 + c0 + tt) * dm.H * dv + (size_t)h * dv + j] = ov;
+            float acc = (ac[0] + ac[1]) + (ac[2] + ac[3]);
+            float rr = (rc[0] + rc[1]) + (rc[2] + rc[3]);
+#pragma unroll
+            for (int o = 1; o < L; o <<= 1) {
+                acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                rr += __shfl_xor_sync(0xffffffffu, rr, o);
+            }
+#pragma unroll
+            for (int i = 0; i < DL_R; ++i) gg[i] *= S[i];          // g S: needs no u
+            const float u = sb.beta[tt] * (*pv - acc);
+            if (live && l == 0) *po = fmaf(sb.kq[tt], u, rr);
+#pragma unroll
+            for (int i = 0; i < DL_R; ++i) S[i] = fmaf(kk[i], u, gg[i]);
+            pk += Dp; pgk += Dp; pgq += Dp; pg += Dp; pv += CC;
+            po += (size_t)dm.H * dv;
         }
+        __syncthreads();
     }
+    pdl_launch_next();
     if (live) {
 #pragma unroll
         for (int i = 0; i < DL_R; ++i) {
@@ -304,7 +394,8 @@ static int check_dims(const DeltaDims& dm) {
 
 // row: [T, W] with row stride ld (dtype), or part: [n_splits, T, W] 32-bit partial sums, W =
 // 2 G d + H dv + H + ra + rg.  conv_w: [2 G d + H dv, taps] 32-bit.  state: [n_slots,
-// state_stride] 32-bit, the convolution's inputs [taps - 1, 2 G d + H dv] at conv_off.
+// state_stride] 32-bit, the convolution's inputs [taps - 1, 2 G d + H dv] at conv_off (a ring:
+// position pp in row pp % (taps - 1)).
 // several != 0: sequences may bring more than one token (a prompt step); the convolution's
 // inputs are then renewed by a launch of its own.  Outputs: qkv [T, 2 G d + H dv] and beta
 // [T, H] 32-bit, low_a [T, ra] and low_g [T, rg] in dtype.
@@ -323,7 +414,7 @@ AGV_API int agv_delta_prepare(const void* row, long long ld, const float* part, 
                 "delta_prepare: the state is too small");
     if (T == 0) return 0;
     const DeltaState st{state, state_stride, conv_off, slots, cu, seq_index, positions};
-    const size_t smem = (size_t)dm.C() * sizeof(float);
+    const size_t smem = (size_t)(dm.C() + dm.W()) * sizeof(float);
 #define AGV_DP(TT)                                                                              \
     do {                                                                                        \
         RowIn<TT> in{(const TT*)row, ld, part, n_splits, (long long)T * dm.W(), dm.W()};        \
@@ -364,13 +455,21 @@ AGV_API int agv_delta_scan(const float* qkv, const float* beta, const float* a,
     while (CC > 32 / L && CC / 2 >= dv) CC >>= 1;
     if (CC < 1) CC = 1;
     const int Dp = L * DL_R;
-    int TCH = 16;
-    while (TCH > 1 && (size_t)TCH * (3 * Dp + CC + 1) * sizeof(float) > 40 * 1024) TCH >>= 1;
-    const size_t smem = (size_t)TCH * (3 * Dp + CC + 1) * sizeof(float);
+    // two buffers of TCH tokens and the decay's bias, within the 48 KB every launch may have
+    int TCH = T <= B ? 1 : 16;             // (a decode step brings a token a sequence)
+    while (TCH > 1 && (2 * scan_buf_floats(TCH, Dp, CC) + Dp) * sizeof(float) > 46 * 1024) TCH >>= 1;
+    const size_t smem = (2 * scan_buf_floats(TCH, Dp, CC) + Dp) * sizeof(float);
+    AGV_REQUIRE(smem <= 48 * 1024, "delta_scan: key heads of %d need too much shared memory", d);
     ScanArgs sa{qkv, beta, a, dt_bias, neg_a, out, L, CC, TCH};
     const DeltaState st{state, state_stride, 0, slots, cu, nullptr, nullptr};
     dim3 grid((unsigned)((dv + CC - 1) / CC), (unsigned)H, (unsigned)B);
-    agv_launch(delta_scan_kernel, grid, (unsigned)(CC * L), smem, stream, sa, dm, st);
+    switch (L) {
+#define AGV_SCAN(LL) case LL: agv_launch_after(delta_scan_kernel<LL>, grid, (unsigned)(CC * L), smem, \
+                                               stream, sa, dm, st); break
+        AGV_SCAN(1); AGV_SCAN(2); AGV_SCAN(4); AGV_SCAN(8); AGV_SCAN(16); AGV_SCAN(32);
+#undef AGV_SCAN
+        default: return agv_fail(-1, "delta_scan: %d lanes a column", L);
+    }
     AGV_LAUNCH_OK("delta_scan_kernel");
     return 0;
 }
