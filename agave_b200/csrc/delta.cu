@@ -157,6 +157,9 @@ delta_conv_state_kernel(RowIn<T> in, DeltaDims dm, DeltaState st) {
 // sequence come through shared memory TCH at a time: k, q and the decay of the head's key
 // channels (padded with zeros to L * 16 rows, which keeps the padded rows of S at zero), the
 // CTA's columns of v, and beta.  L is a template parameter: the shuffle rounds are unrolled.
+// A lane's 16 rows are four quads, quad i of lane l being rows (i * L + l) * 4 .. + 3: the
+// lanes of a column then read consecutive 16 bytes of a token's row, free of bank conflicts
+// (the columns of a warp read the same addresses).
 struct ScanArgs {
     const float* qkv;          // [T, C]: q | k | v, prepared
     const float* beta;         // [T, H]
@@ -165,7 +168,46 @@ struct ScanArgs {
     const float* neg_a;        // [H]: -exp(A_log)
     float* out;                // [T, H * dv]
     int L, CC, TCH;
+    // what does not depend on the state, made by the launch before, [T, H, L * 16] each with
+    // zeros in the padding, and k . q [T, H]
+    float *wk, *wg, *wgk, *wgq, *wkq;
 };
+
+// What a token's step needs besides the state, for every head: k, the decay g = exp(neg_a *
+// softplus(a + bias)), g * k, g * q and k . q.  A warp a (token, head); rows of Dp = L * 16
+// floats, the padding zero, so that the scan copies them 16 bytes at a time.
+__global__ void __launch_bounds__(256)
+delta_decay_kernel(ScanArgs a, DeltaDims dm, int T, int Dp) {
+    pdl_wait();
+    pdl_launch_next();
+    const int lane = threadIdx.x & 31;
+    const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (w >= (long long)T * dm.H) return;
+    const int t = (int)(w / dm.H), h = (int)(w - (long long)t * dm.H), g = h / (dm.H / dm.G);
+    const int d = dm.d;
+    const float* q = a.qkv + (size_t)t * dm.C() + (size_t)g * d;
+    const float* k = q + dm.nq();
+    const float* pre = a.a + ((size_t)t * dm.H + h) * d;
+    const float* bias = a.dt_bias + (size_t)h * d;
+    const float na = a.neg_a[h];
+    const size_t o = (size_t)w * Dp;
+    float s = 0.f;
+    for (int r = lane; r < Dp; r += 32) {
+        float kv = 0.f, gv = 0.f, qv = 0.f;
+        if (r < d) {
+            kv = k[r];
+            qv = q[r];
+            gv = expf(na * softplus_f(pre[r] + bias[r]));
+        }
+        a.wk[o + r] = kv;
+        a.wg[o + r] = gv;
+        a.wgk[o + r] = gv * kv;
+        a.wgq[o + r] = gv * qv;
+        s = fmaf(kv, qv, s);
+    }
+    s = warp_sum(s);
+    if (lane == 0) a.wkq[w] = s;
+}
 
 // A 4-byte asynchronous copy into shared memory (the sources are rows of 32-bit tensors at
 // offsets that need not be multiples of 16 bytes).
@@ -174,14 +216,18 @@ __device__ __forceinline__ void cp_async_f32(float* dst, const float* src) {
                  :: "r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_16(float* dst, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;"
+                 :: "r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" :: "n"(N) : "memory"); }
 
 // The tokens come through two buffers: while the lanes run the recurrence over one, the next
 // TCH tokens' k, q, decay pre-activation, v and beta are on their way (asynchronous copies),
-// so the trip to L2 or HBM is paid once a sequence, not once a buffer.  When a buffer has
-// arrived, what does not depend on the state is made in place: the decay g (bias, softplus,
-// exp), g * k, g * q and the token's k . q.  With them a token is one round of dot products,
+// so the trip to L2 or HBM is paid once a sequence, not once a buffer.  What does not depend
+// on the state was made by the launch before for all tokens at once: the decay g, g * k,
+// g * q and the token's k . q.  With them a token is one round of dot products,
 //
 //      a = (g S)^T k = sum_r S_r (g k)_r      r = (g S)^T q = sum_r S_r (g q)_r
 //      u = beta (v - a);    o = r + (k . q) u;    S <- g S + k u
@@ -215,7 +261,7 @@ delta_scan_kernel(ScanArgs a, DeltaDims dm, DeltaState st) {
     if (slot < 0) return;
     const int t0 = st.cu[b], n = st.cu[b + 1] - t0;
     if (n <= 0) return;
-    const int h = blockIdx.y, g = h / (dm.H / dm.G);
+    const int h = blockIdx.y;
     const int d = dm.d, dv = dm.dv, C = dm.C(), nq = dm.nq();
     constexpr int Dp = L * DL_R;
     const int CC = a.CC, TCH = a.TCH;
@@ -224,23 +270,23 @@ delta_scan_kernel(ScanArgs a, DeltaDims dm, DeltaState st) {
     const int j = blockIdx.x * CC + jc;
     const bool live = jc < CC && j < dv;
     const size_t per = scan_buf_floats(TCH, Dp, CC);
-    float* sdt = smem + 2 * per;                                   // the decay's bias [Dp]
-    for (size_t i = threadIdx.x; i < 2 * per; i += blockDim.x) smem[i] = 0.f;   // the padding stays 0
-    for (int r = threadIdx.x; r < Dp; r += blockDim.x)
-        sdt[r] = r < d ? a.dt_bias[(size_t)h * d + r] : 0.f;
+    // (columns of v past dv are never copied: zero them once)
+    for (size_t i = threadIdx.x; i < 2 * per; i += blockDim.x) smem[i] = 0.f;
     __syncthreads();
 
     auto fetch = [&](int c0, float* base) {
         const int m = min(TCH, n - c0);
         const ScanBuf sb(base, TCH, Dp, CC);
-        for (int idx = threadIdx.x; idx < m * Dp; idx += blockDim.x) {
-            const int tt = idx / Dp, r = idx - tt * Dp;
-            if (r < d) {
-                const size_t t = (size_t)(t0 + c0 + tt);
-                cp_async_f32(sb.gq + idx, a.qkv + t * C + (size_t)g * d + r);          // q
-                cp_async_f32(sb.k + idx, a.qkv + t * C + nq + (size_t)g * d + r);
-                cp_async_f32(sb.g + idx, a.a + t * dm.H * d + (size_t)h * d + r);      // pre-activation
-            }
+        // rows of Dp floats a token: tokens of a head lie H * Dp apart
+        constexpr int Q = Dp / 4;
+        for (int idx = threadIdx.x; idx < m * Q; idx += blockDim.x) {
+            const int tt = idx / Q, c4 = (idx - tt * Q) * 4;
+            const size_t src = ((size_t)(t0 + c0 + tt) * dm.H + h) * Dp + c4;
+            const int dst = tt * Dp + c4;
+            cp_async_16(sb.k + dst, a.wk + src);
+            cp_async_16(sb.g + dst, a.wg + src);
+            cp_async_16(sb.gk + dst, a.wgk + src);
+            cp_async_16(sb.gq + dst, a.wgq + src);
         }
         for (int idx = threadIdx.x; idx < m * CC; idx += blockDim.x) {
             const int tt = idx / CC, c = idx - tt * CC;
@@ -248,8 +294,10 @@ delta_scan_kernel(ScanArgs a, DeltaDims dm, DeltaState st) {
             if (col < dv)
                 cp_async_f32(sb.v + idx, a.qkv + (size_t)(t0 + c0 + tt) * C + 2 * nq + (size_t)h * dv + col);
         }
-        for (int tt = threadIdx.x; tt < m; tt += blockDim.x)
+        for (int tt = threadIdx.x; tt < m; tt += blockDim.x) {
             cp_async_f32(sb.beta + tt, a.beta + (size_t)(t0 + c0 + tt) * dm.H + h);
+            cp_async_f32(sb.kq + tt, a.wkq + (size_t)(t0 + c0 + tt) * dm.H + h);
+        }
         cp_async_commit();
     };
 
@@ -258,11 +306,9 @@ delta_scan_kernel(ScanArgs a, DeltaDims dm, DeltaState st) {
     fetch(0, smem);
 #pragma unroll
     for (int i = 0; i < DL_R; ++i) {
-        const int r = l * DL_R + i;
+        const int r = ((i >> 2) * L + l) * 4 + (i & 3);
         S[i] = live && r < d ? srow[r] : 0.f;
     }
-    const float na = a.neg_a[h];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     int cur = 0;
     for (int c0 = 0; c0 < n; c0 += TCH, cur ^= 1) {
         const int m = min(TCH, n - c0);
@@ -275,28 +321,10 @@ delta_scan_kernel(ScanArgs a, DeltaDims dm, DeltaState st) {
             cp_async_wait<0>();
         }
         __syncthreads();
-        // k . q of each token (a warp a token), before q becomes g * q
-        for (int tt = warp; tt < m; tt += nwarps) {
-            float s = 0.f;
-            for (int r = lane; r < Dp; r += 32) s = fmaf(sb.k[tt * Dp + r], sb.gq[tt * Dp + r], s);
-            s = warp_sum(s);
-            if (lane == 0) sb.kq[tt] = s;
-        }
-        __syncthreads();
-        for (int idx = threadIdx.x; idx < m * Dp; idx += blockDim.x) {
-            const int r = idx % Dp;
-            if (r < d) {
-                const float gv = expf(na * softplus_f(sb.g[idx] + sdt[r]));
-                sb.g[idx] = gv;
-                sb.gk[idx] = gv * sb.k[idx];
-                sb.gq[idx] = gv * sb.gq[idx];
-            }
-        }
-        __syncthreads();
-        const float* pk = sb.k + l * DL_R;
-        const float* pgk = sb.gk + l * DL_R;
-        const float* pgq = sb.gq + l * DL_R;
-        const float* pg = sb.g + l * DL_R;
+        const float* pk = sb.k + l * 4;
+        const float* pgk = sb.gk + l * 4;
+        const float* pgq = sb.gq + l * 4;
+        const float* pg = sb.g + l * 4;
         const float* pv = sb.v + (jc < CC ? jc : 0);
         float* po = a.out + (size_t)(t0 + c0) * dm.H * dv + (size_t)h * dv + (live ? j : 0);
 #pragma unroll 2
@@ -304,8 +332,8 @@ delta_scan_kernel(ScanArgs a, DeltaDims dm, DeltaState st) {
             float gk[DL_R], gq[DL_R], kk[DL_R], gg[DL_R];
 #pragma unroll
             for (int i = 0; i < DL_R / 4; ++i) {
-                const float4 x = reinterpret_cast<const float4*>(pgk)[i];
-                const float4 y = reinterpret_cast<const float4*>(pgq)[i];
+                const float4 x = reinterpret_cast<const float4*>(pgk)[i * L];
+                const float4 y = reinterpret_cast<const float4*>(pgq)[i * L];
                 gk[4 * i] = x.x; gk[4 * i + 1] = x.y; gk[4 * i + 2] = x.z; gk[4 * i + 3] = x.w;
                 gq[4 * i] = y.x; gq[4 * i + 1] = y.y; gq[4 * i + 2] = y.z; gq[4 * i + 3] = y.w;
             }
@@ -317,8 +345,8 @@ delta_scan_kernel(ScanArgs a, DeltaDims dm, DeltaState st) {
             }
 #pragma unroll
             for (int i = 0; i < DL_R / 4; ++i) {
-                const float4 x = reinterpret_cast<const float4*>(pk)[i];
-                const float4 y = reinterpret_cast<const float4*>(pg)[i];
+                const float4 x = reinterpret_cast<const float4*>(pk)[i * L];
+                const float4 y = reinterpret_cast<const float4*>(pg)[i * L];
                 kk[4 * i] = x.x; kk[4 * i + 1] = x.y; kk[4 * i + 2] = x.z; kk[4 * i + 3] = x.w;
                 gg[4 * i] = y.x; gg[4 * i + 1] = y.y; gg[4 * i + 2] = y.z; gg[4 * i + 3] = y.w;
             }
@@ -344,7 +372,7 @@ delta_scan_kernel(ScanArgs a, DeltaDims dm, DeltaState st) {
     if (live) {
 #pragma unroll
         for (int i = 0; i < DL_R; ++i) {
-            const int r = l * DL_R + i;
+            const int r = ((i >> 2) * L + l) * 4 + (i & 3);
             if (r < d) srow[r] = S[i];
         }
     }
@@ -439,10 +467,17 @@ AGV_API int agv_delta_prepare(const void* row, long long ld, const float* part, 
 }
 
 // The recurrence over the step's tokens, sequence by sequence; all tensors 32-bit.
+// work: scratch of agv_delta_scan_work(T, H, d) floats.
+AGV_API long long agv_delta_scan_work(int T, int H, int d) {
+    int L = 1;
+    while (L * DL_R < d) L <<= 1;
+    return (long long)T * H * (4LL * L * DL_R + 1);
+}
+
 AGV_API int agv_delta_scan(const float* qkv, const float* beta, const float* a,
                            const float* dt_bias, const float* neg_a, float* out, int T, int B,
                            int G, int H, int d, int dv, float* state, long long state_stride,
-                           const int* slots, const int* cu, cudaStream_t stream) {
+                           const int* slots, const int* cu, float* work, cudaStream_t stream) {
     const DeltaDims dm{G, H, d, dv, 1, 0, 0};
     if (int rc = check_dims(dm)) return rc;
     AGV_REQUIRE(state && state_stride >= (long long)H * dv * d, "delta_scan: the state is too small");
@@ -457,10 +492,18 @@ AGV_API int agv_delta_scan(const float* qkv, const float* beta, const float* a,
     const int Dp = L * DL_R;
     // two buffers of TCH tokens and the decay's bias, within the 48 KB every launch may have
     int TCH = T <= B ? 1 : 16;             // (a decode step brings a token a sequence)
-    while (TCH > 1 && (2 * scan_buf_floats(TCH, Dp, CC) + Dp) * sizeof(float) > 46 * 1024) TCH >>= 1;
-    const size_t smem = (2 * scan_buf_floats(TCH, Dp, CC) + Dp) * sizeof(float);
+    while (TCH > 1 && 2 * scan_buf_floats(TCH, Dp, CC) * sizeof(float) > 46 * 1024) TCH >>= 1;
+    const size_t smem = 2 * scan_buf_floats(TCH, Dp, CC) * sizeof(float);
     AGV_REQUIRE(smem <= 48 * 1024, "delta_scan: key heads of %d need too much shared memory", d);
-    ScanArgs sa{qkv, beta, a, dt_bias, neg_a, out, L, CC, TCH};
+    AGV_REQUIRE(work && ((size_t)work & 15) == 0, "delta_scan: no scratch, or not 16-byte aligned");
+    const size_t row = (size_t)T * H * Dp;
+    ScanArgs sa{qkv, beta, a, dt_bias, neg_a, out, L, CC, TCH,
+                work, work + row, work + 2 * row, work + 3 * row, work + 4 * row};
+    {
+        const long long warps = (long long)T * H;
+        agv_launch(delta_decay_kernel, (unsigned)((warps + 7) / 8), 256, 0, stream, sa, dm, T, Dp);
+        AGV_LAUNCH_OK("delta_decay_kernel");
+    }
     const DeltaState st{state, state_stride, 0, slots, cu, nullptr, nullptr};
     dim3 grid((unsigned)((dv + CC - 1) / CC), (unsigned)H, (unsigned)B);
     switch (L) {

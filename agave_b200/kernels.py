@@ -835,11 +835,15 @@ def delta_scan(qkv: torch.Tensor, beta: torch.Tensor, a: torch.Tensor, dt_bias: 
     assert dt_bias.numel() == n_heads * head_dim and neg_a.numel() == n_heads
     sp, ss = _state_args(state)
     flops = 6 * T * n_heads * head_dim * value_dim
-    with _span("delta_scan", _nbytes(qkv, beta, a, out), flops):
-        _check(library().agv_delta_scan(_ptr(qkv), _ptr(beta), _ptr(a), _ptr(dt_bias), _ptr(neg_a),
-                                        _ptr(out), T, ctx.batch, n_qk_heads, n_heads, head_dim,
-                                        value_dim, sp, ss, _ptr(ctx.slots), _ptr(ctx.cu_seqlens),
-                                        _stream()))
+    lib = library()
+    lib.agv_delta_scan_work.restype = ctypes.c_longlong
+    # scratch for what does not depend on the state (k, the decay, their products), per head
+    work = ctx.new(int(lib.agv_delta_scan_work(T, n_heads, head_dim)), dtype=torch.float32)
+    with _span("delta_scan", _nbytes(qkv, beta, a, out) + 2 * work.numel() * 4, flops):
+        _check(lib.agv_delta_scan(_ptr(qkv), _ptr(beta), _ptr(a), _ptr(dt_bias), _ptr(neg_a),
+                                  _ptr(out), T, ctx.batch, n_qk_heads, n_heads, head_dim,
+                                  value_dim, sp, ss, _ptr(ctx.slots), _ptr(ctx.cu_seqlens),
+                                  _ptr(work), _stream()))
 
 
 def delta_out(o: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, eps: float, n_heads: int,
