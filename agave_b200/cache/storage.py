@@ -41,12 +41,22 @@ class StateView:
 class Cache:
     def __init__(self, requests: Sequence[object], max_tokens: int, max_seq_len: int,
                  n_slots: int, dtype: torch.dtype, device: torch.device):
+        # an entry asks for keys and values, for fixed-size state, for both (a tuple of the
+        # two requests) or for nothing
         self.requests = list(requests)
         self.dtype, self.device = dtype, device
+
+        def pick(r, kind):
+            for x in (r if isinstance(r, (tuple, list)) else (r,)):
+                if isinstance(x, kind):
+                    return x
+            return None
+        kv_requests = [pick(r, KVRequest) for r in self.requests]
+        state_requests = [pick(r, StateRequest) for r in self.requests]
         max_seq_len = max(1, min(max_seq_len, round_up(max_tokens, PAGE)))
         self.max_seq_len = max_seq_len
         self.max_tokens = max_tokens
-        groups, self.where = plan_groups(self.requests, max_tokens, max_seq_len, n_slots)
+        groups, self.where = plan_groups(kv_requests, max_tokens, max_seq_len, n_slots)
         self.book = CacheBook(groups, n_slots, max_seq_len)
         self.n_slots = n_slots
         self.k_pools: List[torch.Tensor] = []
@@ -63,8 +73,8 @@ class Cache:
         # fixed-size state: one tensor per distinct size
         self.state_where: Dict[int, Tuple[int, int]] = {}
         sizes: Dict[int, List[int]] = {}
-        for entry, r in enumerate(self.requests):
-            if isinstance(r, StateRequest):
+        for entry, r in enumerate(state_requests):
+            if r is not None:
                 sizes.setdefault(r.numel, []).append(entry)
         self.states: List[torch.Tensor] = []
         for numel, entries in sizes.items():

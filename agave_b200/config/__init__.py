@@ -8,6 +8,7 @@ from .gemma3 import Gemma3Config
 from .ramilorn import RamilornConfig
 from .zazerax import ZazeraxConfig
 from .bovozen import BovozenConfig
+from .kadavik import KadavikConfig
 
 __all__ = [
     "AttentionSpec", "BlockSpec", "ConfigError", "GatedFeedForwardSpec", "LayerCall",
@@ -16,5 +17,5 @@ __all__ = [
     "read_config_json", "register_architecture", "registered_architectures",
     "resolve_architecture", "Gemma3Config", "ZazeraxConfig", "DenseFeedForwardSpec",
     "DistanceBiasSpec", "IdentityNormSpec", "LatentAttentionSpec", "WavelengthScalingSpec",
-    "BovozenConfig",
+    "BovozenConfig", "KadavikConfig",
 ]

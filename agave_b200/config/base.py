@@ -35,7 +35,8 @@ class RotarySpec:
     # pairs (2i, 2i + 1) instead of (i, i + rotary_dim/2); a mixer that rotates honours it
     interleaved: bool = False
     # frequencies blended between wavelength bounds, and a multiplier on cos and sin
-    scaling: Optional["WavelengthScalingSpec"] = None
+    # (``WavelengthScalingSpec``), or divided band by band (``BandScalingSpec``)
+    scaling: Optional[object] = None
 
     def key(self) -> Tuple:
         return (self.kind, float(self.theta), float(self.factor), int(self.rotary_dim),
@@ -53,6 +54,18 @@ class WavelengthScalingSpec:
     original: float = 0.0
     fast: float = 32.0
     slow: float = 1.0
+
+
+@dataclass(frozen=True)
+class BandScalingSpec:
+    """Frequency scaling in three bands of wavelength l = 2 pi / f: f is kept where
+    l < original / high, divided by ``factor`` where l > original / low, and between the two,
+    with s = (original / l - low) / (high - low), becomes (1 - s) f / factor + s f.  cos and
+    sin are not multiplied."""
+    factor: float = 1.0
+    original: float = 0.0
+    low: float = 1.0
+    high: float = 4.0
 
 
 @dataclass(frozen=True)
@@ -153,6 +166,17 @@ class AttentionSpec:
     chunk: Optional[int] = None
     distance_slope: Optional[DistanceSlopeSpec] = None
     value_mix: Optional[ValueMixSpec] = None
+    # with ``window``: the sequence's first keep_first keys stay visible behind the window
+    # (position p sees j <= p if p - j < window or j < keep_first), at their true positions
+    keep_first: int = 0
+    # a causal convolution over this many tokens on every channel of q, k and v (tensors
+    # ``q_conv.weight`` ... [channels, taps], no bias, no activation), right after the
+    # projection and before the rotation; 0: none.  The last conv_taps - 1 projected rows of a
+    # sequence are part of its fixed-size state
+    conv_taps: int = 0
+    # the concatenated heads are multiplied element by element by sigmoid(W_g x) (tensor
+    # ``g_proj.weight``) before the output projection
+    out_gate: bool = False
 
     @property
     def v_dim(self) -> int:
@@ -207,6 +231,39 @@ class ChannelDeltaSpec:
 
 
 @dataclass(frozen=True)
+class MatrixMemorySpec:
+    """A recurrent mixer: a matrix memory with exponential gates (the mLSTM of xLSTM).
+
+    q = W_q x * head_dim ** -0.5 and k = W_k x (``n_heads`` heads of ``head_dim``), v = W_v x
+    (heads of ``value_dim``).  Per head a log input gate i = cap * tanh((W_i x + b_i) / cap)
+    and a log forget gate f = logsigmoid(cap * tanh((W_f x + b_f) / cap)), cap = ``gate_cap``.
+    With a running maximum m that starts at 0:  m_t = max(f + m_(t-1), i);
+    S_t = exp(f + m_(t-1) - m_t) S_(t-1) + exp(i - m_t) k v^T;  n_t likewise with k alone;
+    o = S_t^T q / (max(|n_t . q|, exp(-m_t)) + ``den_eps``).  Every head's o is divided by its
+    root mean square (``eps``), the heads are multiplied by a weight per channel and by
+    sigmoid(W_g x) and go through the output product.  S, n and m (32-bit) are a fixed size
+    per sequence."""
+    kind: str = "matrix_memory"
+    n_heads: int = 0
+    head_dim: int = 0
+    value_dim: int = 0
+    gate_cap: float = 15.0
+    eps: float = 1e-6
+    den_eps: float = 1e-6
+
+
+@dataclass(frozen=True)
+class TokenSideSpec:
+    """A per-layer input from the token itself, after the layer's feed-forward: with e the
+    slice [offset, offset + dim) of the token's row of a table shared by the layers
+    (``ModelSpec.token_side_width`` wide), g = gelu_tanh(W_gate h) * e, y = W_proj g and
+    h += y / rms(y) * w (an RMS norm with a plain weight and ``eps``)."""
+    dim: int = 0
+    offset: int = 0
+    eps: float = 1e-6
+
+
+@dataclass(frozen=True)
 class GatedFeedForwardSpec:
     """down(act(gate x) * up x), dense (src/models/gemma3.zig:840-872)."""
     kind: str = "gated_dense"
@@ -241,8 +298,14 @@ class RoutedFeedForwardSpec:
     # a bias [n_experts] added to the router's logits (tensor ``router.bias``)
     router_bias: bool = False
     # "sigmoid": as above; "softmax_top": the logits choose (with ``correction`` False) and the
-    # chosen experts' weights are the softmax over their logits alone
+    # chosen experts' weights are the softmax over their logits alone; "softmax_all": the
+    # scores s are the softmax over all the router's outputs, s + correction chooses, and the
+    # chosen experts' s, divided by their sum (+ 1e-20) and times ``route_scale``, weigh
     weighting: str = "sigmoid"
+    route_scale: float = 1.0
+    # the router has this many outputs beyond ``n_experts``: identity experts without tensors,
+    # whose output is the feed-forward's input itself (times the weight)
+    n_identity: int = 0
     # an expert of the same form that every token uses, of this width (0: none); its output is
     # multiplied by sigmoid(w_sg . x), one number per token (tensor ``shared.gate.weight``)
     shared_size: int = 0
@@ -279,6 +342,8 @@ class BlockSpec:
     kind: str = "sequential"
     # every branch joins the stream times this: h += residual_mult * post(branch(pre(h)))
     residual_mult: float = 1.0
+    # a per-layer input from the token, added after the feed-forward (None: none)
+    token_side: Optional[TokenSideSpec] = None
 
 
 @dataclass(frozen=True)
@@ -288,10 +353,13 @@ class LayerCall:
     ``block`` indexes ``ModelSpec.blocks`` (a block may be called twice);
     ``cache`` names the cache entry the mixer uses and ``writes_cache`` says
     whether this call appends to it (False: it reads what another call wrote).
+    ``state``: the cache entry of the call's own fixed-size state where that is not
+    ``cache`` (a call that reads another's keys and values and still has state of its own).
     """
     block: int
     cache: int
     writes_cache: bool = True
+    state: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -312,9 +380,17 @@ class ModelSpec:
     stream_position: Optional[object] = None
     # logits <- cap * tanh(logits / cap); None: no cap
     logit_softcap: Optional[float] = None
+    # the logits are multiplied by this (before a cap)
+    logit_scale: float = 1.0
+    # width of the table of per-layer token inputs (tensor ``token_side.weight`` [vocab,
+    # width]); the blocks' ``TokenSideSpec`` name their slices.  0: there is none
+    token_side_width: int = 0
 
     def n_cache_entries(self) -> int:
-        return 1 + max(c.cache for c in self.schedule) if self.schedule else 0
+        if not self.schedule:
+            return 0
+        return 1 + max(max(c.cache, c.state if c.state is not None else 0)
+                       for c in self.schedule)
 
 
 def default_schedule(n_blocks: int) -> Tuple[LayerCall, ...]:

@@ -14,6 +14,7 @@
 // Two options beyond that: a value head size hdv that differs from the query / key head
 // size hd, and a sink per query head: a learned logit whose exponential is one more term of
 // the softmax denominator (unscaled; nothing is added to the weighted sum for it).
+// With a sliding window, the sequence's first keep_first keys may stay visible behind it.
 // A bias per (distance, head) may be added to the scaled score, and the cache's value rows
 // may lie at a stride of their own (values that are the leading part of the key rows).
 #include "common.cuh"
@@ -43,7 +44,7 @@ attention_simt_kernel(const T* __restrict__ q, long long q_stride, const T* __re
                       const int* __restrict__ positions, const int* __restrict__ seq_index,
                       const int* __restrict__ cu_seqlens, PagedKV pk, int n_tokens, int nh, int nkv,
                       int hd, float scale, int window, int hdv, long long v_stride,
-                      const float* __restrict__ sinks, DistanceBias db) {
+                      const float* __restrict__ sinks, DistanceBias db, int keep_first) {
     pdl_wait();
     pdl_launch_next();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -73,7 +74,10 @@ attention_simt_kernel(const T* __restrict__ q, long long q_stride, const T* __re
     }
     float m = -INFINITY, l = 0.f;
     const size_t base = PAGED ? 0 : (size_t)cu_seqlens[b];
-    for (int j = lo; j <= p; ++j) {
+    // (with a window, the sequence's first keep_first keys stay visible behind it)
+    const int kept = min(keep_first, lo);
+    for (int j = kept > 0 ? 0 : lo; j <= p; ++j) {
+        if (j == kept && j < lo) j = lo;
         const T *kp, *vp;
         if (PAGED) {
             const int row = j % pk.cap;
@@ -143,7 +147,7 @@ AGV_API int agv_attention_prefill_simt_ex(const void* q, long long q_stride, con
                                           const int* cu_seqlens, int n_tokens, int nh, int nkv,
                                           int hd, float scale, int window, int hdv,
                                           long long v_stride, const float* sinks,
-                                          const float* dist_bias, int n_dist,
+                                          const float* dist_bias, int n_dist, int keep_first,
                                           cudaStream_t stream) {
     if (int rc = check_attn(n_tokens, nh, nkv, hd, window, hdv)) return rc;
     AGV_REQUIRE(!dist_bias || n_dist > 0, "attention: an empty distance table");
@@ -155,11 +159,11 @@ AGV_API int agv_attention_prefill_simt_ex(const void* q, long long q_stride, con
     if (dtype == AGV_F32)
         agv_launch(attention_simt_kernel<float, false>, grid, AT_WARPS * 32, 0, stream, (const float*)q, q_stride, (const float*)k, (const float*)v, kv_stride, (float*)out,
             positions, seq_index, cu_seqlens, pk, n_tokens, nh, nkv, hd, scale, window, hdv,
-            v_stride, sinks, db);
+            v_stride, sinks, db, keep_first);
     else if (dtype == AGV_BF16)
         agv_launch(attention_simt_kernel<__nv_bfloat16, false>, grid, AT_WARPS * 32, 0, stream, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v,
             kv_stride, (__nv_bfloat16*)out, positions, seq_index, cu_seqlens, pk, n_tokens, nh,
-            nkv, hd, scale, window, hdv, v_stride, sinks, db);
+            nkv, hd, scale, window, hdv, v_stride, sinks, db, keep_first);
     else
         return agv_fail(-1, "attention: unknown dtype %d", dtype);
     AGV_LAUNCH_OK("attention_simt_kernel");
@@ -173,7 +177,7 @@ AGV_API int agv_attention_prefill_simt(const void* q, long long q_stride, const 
                                        float scale, int window, cudaStream_t stream) {
     return agv_attention_prefill_simt_ex(q, q_stride, k, v, kv_stride, out, dtype, positions,
                                          seq_index, cu_seqlens, n_tokens, nh, nkv, hd, scale,
-                                         window, hd, kv_stride, nullptr, nullptr, 0, stream);
+                                         window, hd, kv_stride, nullptr, nullptr, 0, 0, stream);
 }
 
 // Queries against the paged cache (the query's own key is already stored).
@@ -186,7 +190,7 @@ AGV_API int agv_attention_paged_simt_ex(const void* q, long long q_stride, void*
                                         const int* positions, const int* seq_index, int max_pages,
                                         int page, int cap, int n_tokens, int nh, int nkv, int hd,
                                         float scale, int window, int hdv, const float* sinks,
-                                        const float* dist_bias, int n_dist, int v_row,
+                                        const float* dist_bias, int n_dist, int v_row, int keep_first,
                                         cudaStream_t stream) {
     if (int rc = check_attn(n_tokens, nh, nkv, hd, window, hdv)) return rc;
     AGV_REQUIRE(!dist_bias || n_dist > 0, "attention: an empty distance table");
@@ -195,16 +199,18 @@ AGV_API int agv_attention_paged_simt_ex(const void* q, long long q_stride, void*
     AGV_REQUIRE(page > 0 && cap > 0 && max_pages > 0, "attention: bad cache geometry");
     AGV_REQUIRE(window <= cap, "attention: window %d exceeds the ring of %d rows",
                 window, cap);
+    AGV_REQUIRE(keep_first >= 0 && (keep_first == 0 || window >= 0),
+                "attention: kept first keys go with a sliding window or none");
     if (n_tokens == 0) return 0;
     const long long items = (long long)n_tokens * nh;
     const unsigned grid = (unsigned)((items + AT_WARPS - 1) / AT_WARPS);
     PagedKV pk{k_pool, v_pool, page_table, slots, max_pages, page, cap, v_row ? v_row : nkv * hdv};
     if (dtype == AGV_F32)
         agv_launch(attention_simt_kernel<float, true>, grid, AT_WARPS * 32, 0, stream, (const float*)q, q_stride, nullptr, nullptr, 0, (float*)out, positions, seq_index,
-            nullptr, pk, n_tokens, nh, nkv, hd, scale, window, hdv, 0LL, sinks, db);
+            nullptr, pk, n_tokens, nh, nkv, hd, scale, window, hdv, 0LL, sinks, db, keep_first);
     else if (dtype == AGV_BF16)
         agv_launch(attention_simt_kernel<__nv_bfloat16, true>, grid, AT_WARPS * 32, 0, stream, (const __nv_bfloat16*)q, q_stride, nullptr, nullptr, 0, (__nv_bfloat16*)out, positions,
-            seq_index, nullptr, pk, n_tokens, nh, nkv, hd, scale, window, hdv, 0LL, sinks, db);
+            seq_index, nullptr, pk, n_tokens, nh, nkv, hd, scale, window, hdv, 0LL, sinks, db, keep_first);
     else
         return agv_fail(-1, "attention: unknown dtype %d", dtype);
     AGV_LAUNCH_OK("attention_simt_kernel");
@@ -219,5 +225,5 @@ AGV_API int agv_attention_paged_simt(const void* q, long long q_stride, void* ou
                                      cudaStream_t stream) {
     return agv_attention_paged_simt_ex(q, q_stride, out, dtype, k_pool, v_pool, page_table, slots,
                                        positions, seq_index, max_pages, page, cap, n_tokens, nh,
-                                       nkv, hd, scale, window, hd, nullptr, nullptr, 0, 0, stream);
+                                       nkv, hd, scale, window, hd, nullptr, nullptr, 0, 0, 0, stream);
 }

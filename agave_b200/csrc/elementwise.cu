@@ -598,3 +598,40 @@ AGV_API int agv_norm_residual(float* h, const void* y, int y_dtype, int n_splits
 #undef AGV_NORM_CASE
     return agv_fail(-1, "norm: unknown dtypes y=%d x=%d", y_dtype, x_dtype);
 }
+
+// ------------------------------------------------------------- gated token rows
+// out[t, i] = gelu_tanh(z[t, i]) * e[t, i]: a per-token row e (32-bit, row stride lde: a
+// slice of a wider gathered table) gated by a projection z of the stream.
+template <typename TZ, typename TO>
+__global__ void gelu_mul_rows_kernel(const TZ* __restrict__ z, const float* __restrict__ e,
+                                     long long lde, TO* __restrict__ out, int n_tokens, int n) {
+    pdl_wait();
+    pdl_launch_next();
+    const long long total = (long long)n_tokens * n;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const long long t = idx / n;
+        const int i = (int)(idx - t * n);
+        const float x = to_f32(z[idx]);
+        const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+        out[idx] = from_f32<TO>(0.5f * x * (1.0f + tanhf(u)) * e[t * lde + i]);
+    }
+}
+
+AGV_API int agv_gelu_mul_rows(const void* z, int z_dtype, const float* e, long long lde, void* out,
+                              int out_dtype, int T, int n, cudaStream_t stream) {
+    AGV_REQUIRE(T >= 0 && n > 0 && lde >= n, "gelu_mul_rows: bad sizes");
+    if (T == 0) return 0;
+    const long long total = (long long)T * n;
+    const unsigned grid = (unsigned)std::min<long long>((total + 255) / 256, 4096);
+#define AGV_GM(TZ, TO)                                                                     \
+    agv_launch(gelu_mul_rows_kernel<TZ, TO>, grid, 256, 0, stream, (const TZ*)z, e, lde,   \
+               (TO*)out, T, n)
+    if (z_dtype == AGV_F32 && out_dtype == AGV_F32) AGV_GM(float, float);
+    else if (z_dtype == AGV_F32 && out_dtype == AGV_BF16) AGV_GM(float, __nv_bfloat16);
+    else if (z_dtype == AGV_BF16 && out_dtype == AGV_BF16) AGV_GM(__nv_bfloat16, __nv_bfloat16);
+    else return agv_fail(-1, "gelu_mul_rows: unknown dtypes z=%d out=%d", z_dtype, out_dtype);
+#undef AGV_GM
+    AGV_LAUNCH_OK("gelu_mul_rows_kernel");
+    return 0;
+}

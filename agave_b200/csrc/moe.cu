@@ -36,24 +36,63 @@ __device__ __forceinline__ float moe_act(float t, int act) {
 constexpr int RT_WARPS = 4;
 constexpr int RT_MAX_E = 512;
 
-// How a logit becomes a score: bias [E] (or null) is added to it first; softmax_top: the
-// score is the logit itself and the chosen experts' weights are the softmax over their
-// logits, else the score, and the weight, is the logit's sigmoid.
+// How a logit becomes a score: bias [E] (or null) is added to it first.  mode 0: the score,
+// and the weight, is the logit's sigmoid.  mode 1 (softmax over the chosen): the score is the
+// logit itself and the chosen experts' weights are the softmax over their logits.  mode 2
+// (softmax over all): the scores are the softmax over all the logits, score + correction
+// chooses, and the chosen experts' scores, divided by their sum (+ 1e-20) and multiplied by
+// `scale`, weigh.
 struct RouteScore {
     const float* bias;
-    int softmax_top;
+    int mode;
+    float scale;
     __device__ __forceinline__ float score(float z, int e) const {
         if (bias) z += bias[e];
-        return softmax_top ? z : 1.0f / (1.0f + expf(-z));
+        return mode ? z : 1.0f / (1.0f + expf(-z));
     }
-    // the chosen experts' scores (their logits) become their softmax, by one thread
-    __device__ __forceinline__ void weigh(float* w, int top) const {
-        if (!softmax_top) return;
-        float m = w[0];
-        for (int k = 1; k < top; ++k) m = fmaxf(m, w[k]);
+    // mode 2, by one thread: s [E] logits become their softmax, c = s + correction
+    __device__ __forceinline__ void spread(float* s, float* c, const float* correction,
+                                           int E) const {
+        if (mode != 2) return;
+        float m = s[0];
+        for (int e = 1; e < E; ++e) m = fmaxf(m, s[e]);
         float sum = 0.f;
-        for (int k = 0; k < top; ++k) { w[k] = expf(w[k] - m); sum += w[k]; }
-        for (int k = 0; k < top; ++k) w[k] /= sum;
+        for (int e = 0; e < E; ++e) { s[e] = expf(s[e] - m); sum += s[e]; }
+        for (int e = 0; e < E; ++e) {
+            s[e] /= sum;
+            c[e] = s[e] + (correction ? correction[e] : 0.f);
+        }
+    }
+    // the same by a warp
+    __device__ __forceinline__ void spread_warp(float* s, float* c, const float* correction,
+                                                int E, int lane) const {
+        if (mode != 2) return;
+        float m = -INFINITY;
+        for (int e = lane; e < E; e += 32) m = fmaxf(m, s[e]);
+        m = warp_max(m);
+        float sum = 0.f;
+        for (int e = lane; e < E; e += 32) { const float x = expf(s[e] - m); s[e] = x; sum += x; }
+        sum = warp_sum(sum);
+        for (int e = lane; e < E; e += 32) {
+            const float x = s[e] / sum;
+            s[e] = x;
+            c[e] = x + (correction ? correction[e] : 0.f);
+        }
+        __syncwarp();
+    }
+    // the chosen experts' scores become their weights, by one thread
+    __device__ __forceinline__ void weigh(float* w, int top) const {
+        if (mode == 1) {
+            float m = w[0];
+            for (int k = 1; k < top; ++k) m = fmaxf(m, w[k]);
+            float sum = 0.f;
+            for (int k = 0; k < top; ++k) { w[k] = expf(w[k] - m); sum += w[k]; }
+            for (int k = 0; k < top; ++k) w[k] /= sum;
+        } else if (mode == 2) {
+            float sum = 0.f;
+            for (int k = 0; k < top; ++k) sum += w[k];
+            for (int k = 0; k < top; ++k) w[k] = w[k] / (sum + 1e-20f) * scale;
+        }
     }
 };
 
@@ -194,8 +233,10 @@ moe_route_kernel(const T* __restrict__ x, long long ldx, const T* __restrict__ w
         }
     }
     __syncwarp();
-    if (lane == 0)
+    if (lane == 0) {
+        rs.spread(s, c, correction, E);
         moe_choose(s, c, E, n_groups, keep, top, ids + (size_t)t * top, wts + (size_t)t * top, rs);
+    }
 }
 
 // 16 bytes of a row as 32-bit values.
@@ -269,6 +310,7 @@ moe_route_tiled_kernel(const T* __restrict__ x, long long ldx, const T* __restri
     __syncthreads();
     if (warp < RT_TOK && t0 + warp < n_tokens) {
         const int t = t0 + warp;
+        rs.spread_warp(smem + (warp * 3) * E, smem + (warp * 3 + 1) * E, correction, E, lane);
         moe_choose_warp(smem + (warp * 3) * E, smem + (warp * 3 + 1) * E,
                         smem + (warp * 3 + 2) * E, E, n_groups, keep, top, ids + (size_t)t * top,
                         wts + (size_t)t * top, lane, rs);
@@ -295,7 +337,8 @@ moe_plan_kernel(const int* __restrict__ ids, const float* __restrict__ wts, int 
     __syncthreads();
     pdl_wait();
     for (int i = threadIdx.x; i < max_rows; i += blockDim.x) tok[i] = -1;
-    for (int p = threadIdx.x; p < P; p += blockDim.x) atomicAdd(&count[ids[p]], 1);
+    for (int p = threadIdx.x; p < P; p += blockDim.x)
+        if (ids[p] < E) atomicAdd(&count[ids[p]], 1);     // (an id beyond the experts: a pair no expert runs)
     __syncthreads();
     if (threadIdx.x == 0) {
         int at = 0;
@@ -326,6 +369,7 @@ moe_plan_kernel(const int* __restrict__ ids, const float* __restrict__ wts, int 
     // whatever the atomics make it, which no result depends on (rows are independent)
     for (int p = threadIdx.x; p < P; p += blockDim.x) {
         const int e = ids[p];
+        if (e >= E) { pos_of[p] = -1; continue; }
         const int pos = start[e] + atomicAdd(&count[e], 1);
         tok[pos] = p / top;
         dst[pos] = (p % top) * n_tokens + p / top;
@@ -425,11 +469,27 @@ moe_grouped_kernel(const TA* __restrict__ A, long long lda, const int* __restric
 // ids, wts: [T, top] outputs.
 // bias: [E] 32-bit or null, added to the logits; softmax_top != 0: the logits choose and the
 // weights are the softmax over the chosen logits (else sigmoids, see the head of this file).
+AGV_API int agv_moe_route_mode(const void* x, long long ldx, const void* wr,
+                               const float* correction, const float* bias, int mode, float scale,
+                               int dtype, int T, int H, int E, int n_groups, int keep, int top,
+                               int* ids, float* wts, cudaStream_t stream);
+
 AGV_API int agv_moe_route_ex(const void* x, long long ldx, const void* wr,
                              const float* correction, const float* bias, int softmax_top,
                              int dtype, int T, int H, int E, int n_groups, int keep, int top,
                              int* ids, float* wts, cudaStream_t stream) {
-    const RouteScore rs{bias, softmax_top};
+    return agv_moe_route_mode(x, ldx, wr, correction, bias, softmax_top ? 1 : 0, 1.0f, dtype, T, H,
+                              E, n_groups, keep, top, ids, wts, stream);
+}
+
+// mode: 0 sigmoid scores, 1 softmax over the chosen logits, 2 softmax over all logits with
+// the chosen scores renormalised and multiplied by `scale` (see RouteScore).
+AGV_API int agv_moe_route_mode(const void* x, long long ldx, const void* wr,
+                               const float* correction, const float* bias, int mode, float scale,
+                               int dtype, int T, int H, int E, int n_groups, int keep, int top,
+                               int* ids, float* wts, cudaStream_t stream) {
+    const RouteScore rs{bias, mode, scale};
+    AGV_REQUIRE(mode >= 0 && mode <= 2, "moe_route: unknown mode %d", mode);
     AGV_REQUIRE(T >= 0 && H > 0 && E > 0 && top > 0, "moe_route: bad sizes");
     AGV_REQUIRE(E <= RT_MAX_E, "moe_route: %d experts exceed %d", E, RT_MAX_E);
     AGV_REQUIRE(n_groups >= 1 && E % n_groups == 0, "moe_route: %d experts do not form %d equal "
@@ -577,5 +637,44 @@ AGV_API int agv_moe_grouped(const void* a, long long lda, const int* a_index, co
     else return agv_fail(-1, "moe_grouped: unsupported dtypes in=%d out=%d", in_dtype, out_dtype);
 #undef AGV_MOE
     AGV_LAUNCH_OK("moe_grouped_kernel");
+    return 0;
+}
+
+// Pairs whose id lies at or beyond the experts are identities: the pair's output is the
+// token's own input times the pair's weight.  y [top, T, H] (32-bit) receives it in the rows
+// the experts' scatter leaves out.
+namespace {
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_identity_kernel(const T* __restrict__ x, long long ldx, const int* __restrict__ ids,
+                    const float* __restrict__ wts, int n_tokens, int top, int E, int H,
+                    float* __restrict__ y) {
+    pdl_wait();
+    pdl_launch_next();
+    const int p = blockIdx.x;
+    if (ids[p] < E) return;
+    const int t = p / top, c = p % top;
+    const float w = wts[p];
+    const T* xr = x + (size_t)t * ldx;
+    float* yr = y + ((size_t)c * n_tokens + t) * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) yr[i] = w * to_f32(xr[i]);
+}
+}  // namespace
+
+AGV_API int agv_moe_identity(const void* x, long long ldx, int dtype, const int* ids,
+                             const float* wts, int T, int top, int E, int H, float* y,
+                             cudaStream_t stream) {
+    AGV_REQUIRE(T >= 0 && top > 0 && E >= 0 && H > 0 && ldx >= H, "moe_identity: bad sizes");
+    if (T == 0) return 0;
+    const unsigned grid = (unsigned)(T * top);
+    if (dtype == AGV_F32)
+        agv_launch(moe_identity_kernel<float>, grid, 256, 0, stream, (const float*)x, ldx, ids, wts,
+                   T, top, E, H, y);
+    else if (dtype == AGV_BF16)
+        agv_launch(moe_identity_kernel<__nv_bfloat16>, grid, 256, 0, stream,
+                   (const __nv_bfloat16*)x, ldx, ids, wts, T, top, E, H, y);
+    else
+        return agv_fail(-1, "moe_identity: unknown dtype %d", dtype);
+    AGV_LAUNCH_OK("moe_identity_kernel");
     return 0;
 }

@@ -46,6 +46,12 @@ class StepContext:
     # what a layer keeps for later layers of the same step, by its cache entry (the values
     # another layer mixes into its own)
     step_values: Dict[int, torch.Tensor] = field(default_factory=dict)
+    # the cache entry of the running call's own fixed-size state (the decoder sets it before
+    # every block: the call's ``state`` entry, or its ``cache`` entry)
+    state_entry: Optional[int] = None
+    # the tokens' rows of the table of per-layer token inputs, 32-bit [T, width], gathered
+    # once a step for all layers (None: the model has no such table)
+    token_side_rows: Optional[torch.Tensor] = None
 
     def new(self, *shape, dtype=None) -> torch.Tensor:
         return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)

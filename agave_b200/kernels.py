@@ -276,12 +276,15 @@ def soft_cap(z: torch.Tensor, cap: float) -> None:
 # ------------------------------------------------------ routed feed-forward
 def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor],
               n_groups: int, keep: int, top: int, ids: torch.Tensor, wts: torch.Tensor,
-              bias: Optional[torch.Tensor] = None, softmax_top: bool = False) -> None:
+              bias: Optional[torch.Tensor] = None, softmax_top: bool = False,
+              softmax_all: bool = False, scale: float = 1.0) -> None:
     """ids, wts [T, top]: the experts each token of x [T, H] uses and their weights.
     s = sigmoid(W_r x) in 32-bit; s + correction chooses (only among the experts of the
     ``keep`` groups, of ``n_groups`` equal ones, whose two largest choice scores sum highest),
     s itself weighs.  ``bias`` [E] (32-bit) is added to the logits first; ``softmax_top``: the
-    logits themselves choose and the weights are the softmax over the chosen logits."""
+    logits themselves choose and the weights are the softmax over the chosen logits;
+    ``softmax_all``: s is the softmax over all the logits, s + correction chooses and the chosen
+    s, divided by their sum (+ 1e-20) and times ``scale``, weigh."""
     T, H = x.shape
     E = w_router.shape[0]
     assert w_router.shape == (E, H) and x.stride(1) == 1 and x.dtype == w_router.dtype
@@ -290,10 +293,39 @@ def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction: Optional[torc
     assert ids.shape == (T, top) and wts.shape == (T, top)
     assert bias is None or bias.shape == (E,)
     with _span("router", _nbytes(x, w_router), 2 * T * E * H):
-        _check(library().agv_moe_route_ex(_ptr(x), ctypes.c_longlong(x.stride(0)), _ptr(w_router),
-                                          _ptr(correction), _ptr(bias), 1 if softmax_top else 0,
-                                          dtype_code(x.dtype), T, H, E, n_groups, keep, top,
-                                          _ptr(ids), _ptr(wts), _stream()))
+        assert not (softmax_top and softmax_all)
+        _check(library().agv_moe_route_mode(
+            _ptr(x), ctypes.c_longlong(x.stride(0)), _ptr(w_router), _ptr(correction), _ptr(bias),
+            2 if softmax_all else 1 if softmax_top else 0, ctypes.c_float(scale),
+            dtype_code(x.dtype), T, H, E, n_groups, keep, top, _ptr(ids), _ptr(wts), _stream()))
+
+
+def moe_identity(x: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, n_experts: int,
+                 y: torch.Tensor) -> None:
+    """For every (token, choice) pair whose id is at or beyond ``n_experts`` (an identity
+    expert): y[choice, token, :] = weight * x[token, :]; y [top, T, H] 32-bit.  The other rows
+    are the experts' to write."""
+    T, H = x.shape
+    top = ids.shape[1]
+    _i32(ids, "ids"); _f32(wts, "wts"); _f32(y, "y"); _dense(ids, "ids"); _dense(wts, "wts")
+    _dense(y, "y")
+    assert x.stride(1) == 1 and ids.shape == wts.shape == (T, top) and y.shape == (top, T, H)
+    with _span("experts_identity", _nbytes(x)):
+        _check(library().agv_moe_identity(_ptr(x), ctypes.c_longlong(x.stride(0)),
+                                          dtype_code(x.dtype), _ptr(ids), _ptr(wts), T, top,
+                                          n_experts, H, _ptr(y), _stream()))
+
+
+def gelu_mul_rows(z: torch.Tensor, e: torch.Tensor, out: torch.Tensor) -> None:
+    """out [T, n] = gelu_tanh(z [T, n]) * e [T, n]; e is 32-bit and may be a column slice of a
+    wider tensor."""
+    T, n = z.shape
+    _f32(e, "e"); _dense(z, "z"); _dense(out, "out")
+    assert e.shape == (T, n) and e.stride(1) == 1 and out.shape == (T, n)
+    with _span("token_side_gate", _nbytes(z, out) + T * n * 4):
+        _check(library().agv_gelu_mul_rows(_ptr(z), dtype_code(z.dtype), _ptr(e),
+                                           ctypes.c_longlong(e.stride(0)), _ptr(out),
+                                           dtype_code(out.dtype), T, n, _stream()))
 
 
 def row_gate(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor) -> None:
@@ -570,7 +602,8 @@ def attention_prefill_simt(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, ou
                            cu_seqlens: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
                            scale: float, window: int, value_dim: int = 0,
                            sinks: Optional[torch.Tensor] = None,
-                           dist_bias: Optional[torch.Tensor] = None) -> None:
+                           dist_bias: Optional[torch.Tensor] = None,
+                           keep_first: int = 0) -> None:
     """Prompts that start at 0; q [T, nh*hd], k [T, nkv*hd], v [T, nkv*hdv] row-strided
     views (hdv = value_dim or head_dim), out [T, nh*hdv]; ``sinks`` [nh]: a logit per query
     head that joins its softmax denominator once; ``dist_bias`` [nh, n]: added to the scaled
@@ -588,7 +621,7 @@ def attention_prefill_simt(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, ou
         _ptr(seq_index), _ptr(cu_seqlens), T, n_heads, n_kv_heads, head_dim,
         ctypes.c_float(scale), window, value_dim or head_dim, ctypes.c_longlong(v.stride(0)),
         _ptr(sinks), _ptr(dist_bias), dist_bias.shape[1] if dist_bias is not None else 0,
-        _stream()))
+        int(keep_first), _stream()))
 
 
 def attention_paged_simt(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor,
@@ -597,7 +630,8 @@ def attention_paged_simt(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tenso
                          n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
                          window: int, value_dim: int = 0,
                          sinks: Optional[torch.Tensor] = None,
-                         dist_bias: Optional[torch.Tensor] = None, v_row: int = 0) -> None:
+                         dist_bias: Optional[torch.Tensor] = None, v_row: int = 0,
+                         keep_first: int = 0) -> None:
     """Queries against the paged cache; their own keys are already stored.  ``v_row``: the
     elements between two positions' value rows where that is not nkv * hdv (values that are
     the leading part of the key rows: v_pool is then k_pool)."""
@@ -617,7 +651,8 @@ def attention_paged_simt(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tenso
         _ptr(v_pool), _ptr(page_table), _ptr(slots), _ptr(positions), _ptr(seq_index),
         page_table.shape[1], page, cap, T, n_heads, n_kv_heads, head_dim,
         ctypes.c_float(scale), window, value_dim or head_dim, _ptr(sinks), _ptr(dist_bias),
-        dist_bias.shape[1] if dist_bias is not None else 0, int(v_row), _stream()))
+        dist_bias.shape[1] if dist_bias is not None else 0, int(v_row), int(keep_first),
+        _stream()))
 
 
 # ------------------------------------------- rows of stacked projections, latent attention
@@ -858,6 +893,122 @@ def delta_out(o: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, eps: float, 
         _check(library().agv_delta_out(_ptr(o), _ptr(gate), _ptr(w), ctypes.c_float(eps), T,
                                        n_heads, value_dim, _ptr(ctx.seq_index), _ptr(ctx.slots),
                                        _ptr(y), dtype_code(y.dtype), _stream()))
+
+
+
+# ------------------------------------------------------- matrix memory (mLSTM)
+def mlstm_state_numel(n_heads: int, head_dim: int, value_dim: int) -> int:
+    """32-bit values a sequence's matrix memory takes: S [H, d, dv], n [H, d], m [H]."""
+    return n_heads * head_dim * value_dim + n_heads * head_dim + n_heads
+
+
+def _f32_row_input(row, partial, T, W):
+    """(row pointer, stride, partial pointer, n_splits) of a 32-bit stacked projection."""
+    if partial is not None:
+        _f32(partial, "partial"); _dense(partial, "partial")
+        assert partial.dim() == 3 and partial.shape[1:] == (T, W)
+        return ctypes.c_void_p(0), ctypes.c_longlong(0), _ptr(partial), partial.shape[0]
+    _f32(row, "row")
+    assert row.shape == (T, W) and row.stride(1) == 1
+    return _ptr(row), ctypes.c_longlong(row.stride(0)), ctypes.c_void_p(0), 0
+
+
+def mlstm_prepare(row: Optional[torch.Tensor], partial: Optional[torch.Tensor], T: int,
+                  n_heads: int, head_dim: int, value_dim: int, bias_i: torch.Tensor,
+                  bias_f: torch.Tensor, cap: float, q_mult: float, qkv: torch.Tensor,
+                  gates: torch.Tensor) -> None:
+    """From a token's row  q | k | v | g | i | f  of the stacked projection (32-bit [T, W] or
+    ``partial`` [S, T, W]): qkv [T, 2 H d + H dv] = q * q_mult | k | v and gates [T, 2 H] =
+    the log input gates cap * tanh((i + b_i) / cap), then the log forget gates
+    logsigmoid(cap * tanh((f + b_f) / cap)); all 32-bit."""
+    H, d, dv = n_heads, head_dim, value_dim
+    W = 2 * H * d + 2 * H * dv + 2 * H
+    rp, ld, pp, ns = _f32_row_input(row, partial, T, W)
+    for t, n in ((bias_i, "bias_i"), (bias_f, "bias_f"), (qkv, "qkv"), (gates, "gates")):
+        _f32(t, n); _dense(t, n)
+    assert qkv.shape == (T, 2 * H * d + H * dv) and gates.shape == (T, 2 * H)
+    assert bias_i.numel() == H and bias_f.numel() == H
+    with _span("mlstm_prepare", _nbytes(row, partial, qkv, gates)):
+        _check(library().agv_mlstm_prepare(rp, ld, pp, ns, T, H, d, dv, _ptr(bias_i),
+                                           _ptr(bias_f), ctypes.c_float(cap),
+                                           ctypes.c_float(q_mult), _ptr(qkv), _ptr(gates),
+                                           _stream()))
+
+
+def mlstm_scan(qkv: torch.Tensor, gates: torch.Tensor, out: torch.Tensor, ctx,
+               state: torch.Tensor, n_heads: int, head_dim: int, value_dim: int,
+               den_eps: float) -> None:
+    """The recurrence  m' = max(f + m, i); S <- exp(f + m - m') S + exp(i - m') k v^T; n likewise
+    with k; o = S^T q / (max(|n . q|, exp(-m')) + den_eps)  over the step's tokens, sequence by
+    sequence; S, n and m of each sequence are read from and written to ``state``.  All 32-bit;
+    out [T, H * dv]."""
+    T = qkv.shape[0]
+    H, d, dv = n_heads, head_dim, value_dim
+    for t, n in ((qkv, "qkv"), (gates, "gates"), (out, "out")):
+        _f32(t, n); _dense(t, n)
+    assert qkv.shape == (T, 2 * H * d + H * dv) and gates.shape == (T, 2 * H)
+    assert out.shape == (T, H * dv)
+    sp, ss = _state_args(state)
+    with _span("mlstm_scan", _nbytes(qkv, gates, out), 6 * T * H * d * dv):
+        _check(library().agv_mlstm_scan(_ptr(qkv), _ptr(gates), _ptr(out), T, ctx.batch, H, d, dv,
+                                        ctypes.c_float(den_eps), sp, ss, _ptr(ctx.slots),
+                                        _ptr(ctx.cu_seqlens), _stream()))
+
+
+def mlstm_out(o: torch.Tensor, row: Optional[torch.Tensor], partial: Optional[torch.Tensor],
+              weight: torch.Tensor, eps: float, n_heads: int, head_dim: int, value_dim: int,
+              y: torch.Tensor) -> None:
+    """y[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * weight[h, :] * sigmoid(g[t, h, :]), g the
+    gate's logits in the stacked projection (``row`` / ``partial`` as in ``mlstm_prepare``);
+    o 32-bit [T, H * dv], y in the compute dtype."""
+    T = o.shape[0]
+    H, d, dv = n_heads, head_dim, value_dim
+    rp, ld, pp, ns = _f32_row_input(row, partial, T, 2 * H * d + 2 * H * dv + 2 * H)
+    _f32(o, "o"); _f32(weight, "weight"); _dense(o, "o"); _dense(weight, "weight"); _dense(y, "y")
+    assert o.shape == y.shape == (T, H * dv) and weight.numel() == H * dv
+    with _span("mlstm_out", _nbytes(o, y) + T * H * dv * 4):
+        _check(library().agv_mlstm_out(_ptr(o), rp, ld, pp, ns, _ptr(weight), ctypes.c_float(eps),
+                                       T, H, d, dv, _ptr(y), dtype_code(y.dtype), _stream()))
+
+
+# ------------------------------------------- attention with a short convolution
+def conv_rope_store(row: Optional[torch.Tensor], partial: Optional[torch.Tensor],
+                    out: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
+                    value_dim: int, taps: int, conv_w: torch.Tensor,
+                    cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rotary_dim: int,
+                    gate: bool, state: Optional[torch.Tensor], state_off: int, ctx,
+                    view=None) -> None:
+    """From a token's row  q | k | v | g  of the stacked projection (32-bit rows or partial
+    sums; k and v absent when ``n_kv_heads`` is 0, g without ``gate``): a causal convolution
+    over ``taps`` tokens on every channel of q, k and v (earlier inputs from the step's rows
+    or, before the step, from the ring in ``state`` at ``state_off``, which is brought up to
+    date), the rotation of the first ``rotary_dim`` dimensions of every q and k head, the store
+    of k and v in the cache entry ``view``; out [T, W] receives q | k | v | g in the compute
+    dtype."""
+    T, W = out.shape
+    C = n_heads * head_dim + n_kv_heads * (head_dim + value_dim)
+    assert W == C + (n_heads * value_dim if gate else 0) and out.stride(1) == 1
+    rp, ld, pp, ns = _f32_row_input(row, partial, T, W)
+    _f32(conv_w, "conv_w"); _dense(conv_w, "conv_w"); _f32(cos, "cos"); _f32(sin, "sin")
+    assert conv_w.shape == (C, taps)
+    if rotary_dim:
+        _dense(cos, "cos"); _dense(sin, "sin")
+        assert cos.shape == (T, rotary_dim // 2) and sin.shape == cos.shape
+    if state is not None:
+        sp, ss = _state_args(state)
+    else:
+        sp, ss = ctypes.c_void_p(0), ctypes.c_longlong(0)
+    cache = _cache_args(view, ctx)
+    if view is None:
+        cache[3:6] = [_ptr(ctx.slots), _ptr(ctx.lens), _ptr(ctx.seq_index)]
+    else:
+        assert view.k_pool.dtype == out.dtype
+    with _span("conv_rope_store", _nbytes(row, partial, out)):
+        _check(library().agv_conv_rope_store(
+            rp, ld, pp, ns, dtype_code(out.dtype), T, n_heads, n_kv_heads, head_dim, value_dim,
+            taps, _ptr(conv_w), _ptr(cos), _ptr(sin), rotary_dim, 1 if gate else 0, sp, ss,
+            ctypes.c_longlong(state_off), _ptr(ctx.cu_seqlens), _ptr(ctx.positions), *cache,
+            _ptr(out), ctypes.c_longlong(out.stride(0)), _stream()))
 
 
 # ------------------------------------------------------------------- sampling
@@ -1278,7 +1429,7 @@ def attention_prefill_wants_transposed_values(qkv: torch.Tensor, head_dim: int,
 
 def attention_prefill(q, k, v, out, ctx, n_heads, n_kv_heads, head_dim, scale, window,
                       vt=None, value_dim: int = 0, sinks=None, dist_bias=None,
-                      op: str = "attention") -> None:
+                      op: str = "attention", keep_first: int = 0) -> None:
     """Prompt attention of one layer in bfloat16: the tcgen05 kernel for head sizes
     in steps of 16 up to 256, the mma.sync kernel for the other multiples of 8; else
     (and for value heads of another size than the keys') the one-warp-per-(token, head)
@@ -1289,8 +1440,14 @@ def attention_prefill(q, k, v, out, ctx, n_heads, n_kv_heads, head_dim, scale, w
                q.data_ptr() % 16 == 0 and k.data_ptr() % 16 == 0 and v.data_ptr() % 16 == 0)
     # the tcgen05 kernel does not know value heads of their own size
     same = hdv == head_dim and k.stride(0) == v.stride(0)
+    if not window:
+        keep_first = 0                    # (without a window every key is visible anyway)
     with _span(op, *_attention_cost(ctx, q, k, v, out, n_heads, head_dim, window)):
-        if (aligned and same and head_dim % 16 == 0 and _PREFILL_TC and scale > 0 and
+        if keep_first:
+            attention_prefill_simt(q, k, v, out, ctx.positions, ctx.seq_index, ctx.cu_seqlens,
+                                   n_heads, n_kv_heads, head_dim, scale, window, value_dim=hdv,
+                                   sinks=sinks, dist_bias=dist_bias, keep_first=keep_first)
+        elif (aligned and same and head_dim % 16 == 0 and _PREFILL_TC and scale > 0 and
                 q.shape[0] > PREFILL_TC_MIN_TOKENS):
             attention_prefill_tc(q, k, v, out, ctx.cu_seqlens, ctx.max_new, n_heads, n_kv_heads,
                                  head_dim, scale, window, vt=vt, sinks=sinks, dist_bias=dist_bias)
@@ -1467,14 +1624,18 @@ def attention_decode_fused(partial: torch.Tensor, wq: Optional[torch.Tensor],
 
 def attention_decode(q, out, view, ctx, n_heads, n_kv_heads, head_dim, scale, window,
                      value_dim: int = 0, sinks=None, dist_bias=None,
-                     values_in_keys: bool = False, op: str = "attention") -> None:
+                     values_in_keys: bool = False, op: str = "attention",
+                     keep_first: int = 0) -> None:
     """Decode attention of one layer: the split kernel for head sizes in steps of
     16 up to 512, else (and for value heads of another size than the keys') the
     one-warp-per-head kernel."""
     hdv = value_dim or head_dim
+    if not window:
+        keep_first = 0
     with _span(op, *_attention_cost(ctx, q, None, None, out, n_heads, head_dim, window,
                                     n_kv_heads)):
-        if head_dim % 16 == 0 and head_dim <= 512 and hdv == head_dim and not values_in_keys:
+        if (head_dim % 16 == 0 and head_dim <= 512 and hdv == head_dim and not values_in_keys
+                and not keep_first):
             max_keys = min(abs(window), ctx.max_len) if window else ctx.max_len
             attention_decode_split(q, out, view.k_pool, view.v_pool, view.page_table, ctx.slots,
                                    ctx.positions, view.page, view.cap, n_heads, n_kv_heads,
@@ -1485,4 +1646,5 @@ def attention_decode(q, out, view, ctx, n_heads, n_kv_heads, head_dim, scale, wi
                                  ctx.positions, ctx.seq_index, view.page, view.cap, n_heads,
                                  n_kv_heads, head_dim, scale, window, value_dim=hdv, sinks=sinks,
                                  dist_bias=dist_bias,
-                                 v_row=n_kv_heads * head_dim if values_in_keys else 0)
+                                 v_row=n_kv_heads * head_dim if values_in_keys else 0,
+                                 keep_first=keep_first)

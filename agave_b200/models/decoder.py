@@ -37,6 +37,9 @@ def decoder_param_specs(spec: ModelSpec) -> Dict[str, ParamSpec]:
         S = stream_position_class(spec.stream_position.kind)
         for k, v in S.param_specs(spec.stream_position, spec.hidden_size).items():
             out[f"stream_position.{k}"] = v
+    if getattr(spec, "token_side_width", 0):
+        out["token_side.weight"] = ParamSpec((spec.vocab_size, spec.token_side_width),
+                                             "embedding")
     N = norm_class(spec.final_norm.kind)
     for k, v in N.param_specs(spec.final_norm, spec.hidden_size).items():
         out[f"final_norm.{k}"] = v
@@ -60,6 +63,8 @@ class DecoderModel:
         self.final_norm = norm_class(spec.final_norm.kind)(spec.final_norm, spec.hidden_size,
                                                            dtype, device)
         self.embed_table: Optional[torch.Tensor] = None
+        self.token_side_table: Optional[torch.Tensor] = None
+        self.logit_scale = float(getattr(spec, "logit_scale", 1.0))
         self.head: Optional[Linear] = None
         self.native = None             # the C++ host side of a step, if the model allows it
         self.standard = False          # every block the standard arrangement of the library's parts
@@ -84,6 +89,14 @@ class DecoderModel:
         out: List[object] = [None] * n
         for entry, block in self._writers.items():
             out[entry] = self.blocks[block].cache_request()
+        for call in self.spec.schedule:
+            # a call with state of its own beside the cache entry it reads
+            st = getattr(call, "state", None)
+            if st is None or st == call.cache:
+                continue
+            if out[st] is not None:
+                raise ValueError(f"cache entry {st} is asked for twice")
+            out[st] = self.blocks[call.block].state_request()
         return out
 
     # --------------------------------------------------------------- weights
@@ -101,8 +114,17 @@ class DecoderModel:
             p = "stream_position."
             self.stream_position.load({k[len(p):]: v for k, v in tensors.items()
                                        if k.startswith(p)}, dev)
+        if getattr(self.spec, "token_side_width", 0):
+            self.token_side_table = tensors["token_side.weight"].to(device=dev,
+                                                                    dtype=dt).contiguous()
         p = "final_norm."
         self.final_norm.load({k[len(p):]: v for k, v in tensors.items() if k.startswith(p)}, dev)
+        if self.logit_scale != 1.0:
+            # logits = scale * (E . norm(h) w) = E . norm(h) (scale w): the multiplier joins
+            # the final norm's weight, so no launch and no pass over the logits is spent on it
+            if not hasattr(self.final_norm, "weight") or self.final_norm.weight is None:
+                raise ValueError("a logit multiplier needs a final norm with a weight")
+            self.final_norm.weight = (self.final_norm.weight * self.logit_scale).contiguous()
         if self.spec.tie_embeddings:
             self.head = Linear(self.embed_table, role="lm_head")
         else:
@@ -130,7 +152,7 @@ class DecoderModel:
                 for v in vars(o).values():
                     visit(v)
         visit(self.blocks); visit(self.final_norm); visit(self.embed_table); visit(self.head)
-        visit(self.stream_position)
+        visit(self.stream_position); visit(self.token_side_table)
         return n
 
     # --------------------------------------------------------------- forward
@@ -221,6 +243,9 @@ class DecoderModel:
         kernels.embed(ctx.tokens, self.embed_table, spec.embed_scale, h)
         if self.stream_position is not None:
             self.stream_position.forward(h, ctx)
+        if self.token_side_table is not None:
+            ctx.token_side_rows = ctx.new(T, spec.token_side_width, dtype=torch.float32)
+            kernels.embed(ctx.tokens, self.token_side_table, 1.0, ctx.token_side_rows)
         sched = spec.schedule
         if not sched:
             return h
@@ -232,6 +257,8 @@ class DecoderModel:
             if ctx.cancel is not None and ctx.cancel.is_set():
                 raise Cancelled(f"cancelled before block {i} of {len(sched)}")
             nxt = self.blocks[sched[i + 1].block].entry_norm if i + 1 < len(sched) else None
+            st = getattr(call, "state", None)
+            ctx.state_entry = call.cache if st is None else st
             x = self.blocks[call.block].forward(h, x, ctx, call.cache, call.writes_cache, nxt)
         return h
 

@@ -89,6 +89,11 @@ def standard_blocks(model) -> bool:
         # value heads of their own size, a multiplier on the branches
         if not getattr(b.mixer, "plain", True) or getattr(b, "mult", 1.0) != 1.0:
             return False
+        if getattr(b, "side", None) is not None:
+            return False
+    if getattr(model, "token_side_table", None) is not None or \
+            getattr(model, "logit_scale", 1.0) != 1.0:
+        return False
     return type(model.final_norm) is RMSNorm and model.spec.logit_softcap is None
 
 

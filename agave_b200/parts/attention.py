@@ -33,7 +33,13 @@ row per distance); a bias that falls linearly with distance at a slope per head
 (``distance_slope``: the same table, filled from the slopes); a mask of blocks counted from
 position 0 instead of a sliding window (``chunk``: the kernels take it as a negative window,
 the cache as a ring that holds one block); values mixed with an earlier layer's of the same
-token before they are cached (``value_mix``; tensor ``value_mix``, a scalar).
+token before they are cached (``value_mix``; tensor ``value_mix``, a scalar); the sequence's
+first keys kept visible behind a sliding window (``keep_first``: the cache then keeps every
+key); a short causal convolution over time on every channel of q, k and v, between the
+projection and the rotation (``conv_taps``; tensors ``q_conv.weight`` ...; the last
+conv_taps - 1 projected rows of a sequence live in its fixed-size state, so such a layer asks
+the cache for keys and values *and* for state); and an output gate sigmoid(W_g x) on the
+concatenated heads (``out_gate``; tensor ``g_proj.weight``, stacked under q | k | v).
 """
 from __future__ import annotations
 
@@ -45,7 +51,7 @@ import torch
 from .. import kernels
 from ..config.base import AttentionSpec
 from ..engine.batch import DECODE, PREFILL
-from .base import KVRequest, ParamSpec, position_class, register_mixer
+from .base import KVRequest, ParamSpec, StateRequest, position_class, register_mixer
 from .linear import Linear
 
 
@@ -76,6 +82,19 @@ class AttentionMixer:
         self.chunk = getattr(spec, "chunk", None)
         self.value_mix = getattr(spec, "value_mix", None)
         self.mix_weight = 0.0
+        self.keep_first = int(getattr(spec, "keep_first", 0) or 0)
+        self.conv_taps = int(getattr(spec, "conv_taps", 0) or 0)
+        self.out_gate = bool(getattr(spec, "out_gate", False))
+        self.conv_w: Optional[torch.Tensor] = None
+        if self.keep_first < 0 or self.conv_taps < 0:
+            raise ValueError("keep_first and conv_taps cannot be negative")
+        if self.keep_first and self.chunk is not None:
+            raise ValueError("kept first keys go with a sliding window, not with a mask of blocks")
+        if (self.conv_taps or self.out_gate) and (
+                spec.qk_norm is not None or self.q_temp is not None or self.value_mix is not None
+                or (self.position is not None and getattr(self.position, "interleaved", False))):
+            raise ValueError("a convolution on q, k and v or an output gate goes without q/k "
+                             "norms, a query temperature or mixed values")
         if self.chunk is not None and (self.chunk < 1 or spec.window is not None):
             raise ValueError("a mask of blocks needs a positive size and goes without a window")
         if self.slope_spec is not None and (self.dist_spec is not None or
@@ -98,7 +117,8 @@ class AttentionMixer:
                       and not getattr(spec, "sink", False) and not self.whole_norm
                       and self.dist_spec is None and self.fixed_sink is None
                       and self.slope_spec is None and self.chunk is None
-                      and self.value_mix is None)
+                      and self.value_mix is None and not self.keep_first
+                      and not self.conv_taps and not self.out_gate)
 
     @classmethod
     def param_specs(cls, spec: AttentionSpec, hidden_size: int) -> Dict[str, ParamSpec]:
@@ -125,6 +145,14 @@ class AttentionMixer:
             p["distance_bias"] = ParamSpec((db.rows, spec.n_heads), "float32")
         if getattr(spec, "value_mix", None) is not None:
             p["value_mix"] = ParamSpec((), "float32")
+        taps = int(getattr(spec, "conv_taps", 0) or 0)
+        if taps:
+            p["q_conv.weight"] = ParamSpec((q, taps), "float32")
+            if own_kv:
+                p["k_conv.weight"] = ParamSpec((kv, taps), "float32")
+                p["v_conv.weight"] = ParamSpec((spec.n_kv_heads * vd, taps), "float32")
+        if getattr(spec, "out_gate", False):
+            p["g_proj.weight"] = ParamSpec((spec.n_heads * vd, hidden_size))
         return p
 
     @staticmethod
@@ -144,10 +172,27 @@ class AttentionMixer:
     def cache_request(self):
         if not self.own_kv:
             return None
-        # (a mask of blocks needs the keys of one block: a ring of that many rows)
-        return KVRequest(self.spec.n_kv_heads, self.spec.head_dim,
-                         self.chunk if self.chunk is not None else self.spec.window,
-                         0 if self.value_dim == self.spec.head_dim else self.value_dim)
+        # (a mask of blocks needs the keys of one block: a ring of that many rows; a window
+        # behind which the first keys stay visible keeps every key)
+        window = self.chunk if self.chunk is not None else self.spec.window
+        if self.keep_first:
+            window = None
+        kv = KVRequest(self.spec.n_kv_heads, self.spec.head_dim, window,
+                       0 if self.value_dim == self.spec.head_dim else self.value_dim)
+        st = self.state_request()
+        return kv if st is None else (kv, st)
+
+    def state_request(self):
+        """The fixed-size state of a sequence: the convolution's last conv_taps - 1 inputs (a
+        layer without keys and values of its own keeps those of its queries)."""
+        if self.conv_taps <= 1:
+            return None
+        return StateRequest((self.conv_taps - 1) * self._conv_channels())
+
+    def _conv_channels(self) -> int:
+        s = self.spec
+        n_own = s.n_kv_heads if self.own_kv else 0
+        return s.n_heads * s.head_dim + n_own * (s.head_dim + self.value_dim)
 
     def load(self, tensors: Dict[str, torch.Tensor], dtype: torch.dtype,
              device: torch.device) -> None:
@@ -155,11 +200,23 @@ class AttentionMixer:
             return tensors[name].to(device=device, dtype=dtype)
         # one product for q | k | v: rows of q first, then k, then v (q alone for a layer
         # without keys and values of its own)
+        stack = [mat("q_proj.weight")]
         if self.own_kv:
-            self.qkv = Linear(torch.cat([mat("q_proj.weight"), mat("k_proj.weight"),
-                                         mat("v_proj.weight")], dim=0).contiguous(), role="qkv")
-        else:
-            self.qkv = Linear(mat("q_proj.weight").contiguous(), role="qkv")
+            stack += [mat("k_proj.weight"), mat("v_proj.weight")]
+        if self.out_gate:
+            stack.append(mat("g_proj.weight"))
+        self.qkv = Linear(torch.cat(stack, dim=0).contiguous() if len(stack) > 1 else
+                          stack[0].contiguous(), role="qkv")
+        if self.conv_taps or self.out_gate:
+            def f32(name):
+                return tensors[name].to(device=device, dtype=torch.float32)
+            if self.conv_taps:
+                names = ["q_conv.weight"] + (["k_conv.weight", "v_conv.weight"]
+                                             if self.own_kv else [])
+                self.conv_w = torch.cat([f32(n) for n in names], dim=0).contiguous()
+            else:
+                self.conv_w = torch.ones((self._conv_channels(), 1), dtype=torch.float32,
+                                         device=device)
         self.out = Linear(mat("o_proj.weight").contiguous(), role="out_proj")
         if self.spec.qk_norm is not None:
             add = 1.0 if self.spec.qk_norm.zero_centered else 0.0
@@ -198,6 +255,8 @@ class AttentionMixer:
             self.mix_weight = float(tensors["value_mix"].to(torch.float32).reshape(()).item())
 
     def forward(self, x: torch.Tensor, ctx, cache_entry: int, writes_cache: bool) -> torch.Tensor:
+        if self.conv_taps or self.out_gate:
+            return self._forward_conv(x, ctx, cache_entry, writes_cache)
         if not self.plain:
             return self._forward_options(x, ctx, cache_entry, writes_cache)
         s = self.spec
@@ -290,7 +349,7 @@ class AttentionMixer:
         proj = self.qkv.partial(x, cheap_sum=True)
         part = proj if proj.dim() == 3 else None
         if (ctx.mode == DECODE and part is not None and hdv == hd and not self.whole_norm and
-                self.dist_bias is None and
+                self.dist_bias is None and not self.keep_first and
                 kernels.attention_decode_fused_supported(self.dtype, hd, rotary_dim)):
             out = ctx.new(T, nh * hdv)
             kernels.attention_decode_fused(part, self.q_norm_weight, self.k_norm_weight, eps, cos,
@@ -334,10 +393,72 @@ class AttentionMixer:
             else:
                 k, v, vt = ctx.step_kv[cache_entry]
             kernels.attention_prefill(q, k, v, out, ctx, nh, nkv, hd, s.scale, window, vt=vt,
-                                      value_dim=hdv, sinks=self.sinks, dist_bias=self.dist_bias)
+                                      value_dim=hdv, sinks=self.sinks, dist_bias=self.dist_bias,
+                                      keep_first=self.keep_first)
         else:
             kernels.attention_decode(q, out, view, ctx, nh, nkv, hd, s.scale, window,
-                                     value_dim=hdv, sinks=self.sinks, dist_bias=self.dist_bias)
+                                     value_dim=hdv, sinks=self.sinks, dist_bias=self.dist_bias,
+                                     keep_first=self.keep_first)
+        return self.out.partial(out)
+
+    def _forward_conv(self, x: torch.Tensor, ctx, cache_entry: int,
+                      writes_cache: bool) -> torch.Tensor:
+        """The flow of a layer with a convolution on q, k and v or an output gate: one stacked
+        product q | k | v | g into 32-bit sums; one row kernel (convolution from the step's
+        rows and the sequence's stored inputs, rotation, cache store, everything rounded once);
+        attention from the step's tensors (prompts) or the cache (decoding); the gate; the
+        output product."""
+        from .matrix_memory import project_f32
+        s = self.spec
+        nh, nkv, hd, hdv = s.n_heads, s.n_kv_heads, s.head_dim, self.value_dim
+        if writes_cache != self.own_kv:
+            raise ValueError("a layer without key / value projections must read another call's "
+                             "cache entry, and one with them must write its own")
+        T = x.shape[0]
+        cos = sin = None
+        rotary_dim = 0
+        if self.position is not None:
+            cos, sin = self.position.tables(ctx)
+            rotary_dim = self.position.rotary_dim
+        view = ctx.cache.kv_view(cache_entry)
+        window = s.window or 0
+        if self.chunk is not None:
+            window = -int(self.chunk)
+        if abs(window) >= ctx.cache.max_seq_len:
+            window = 0
+        n_own = nkv if self.own_kv else 0
+        C = (nh + n_own) * hd + n_own * hdv
+        row, part = project_f32(self.qkv, x)
+        qkvg = ctx.new(T, C + (nh * hdv if self.out_gate else 0))
+        state = None
+        taps = max(self.conv_taps, 1)
+        if taps > 1:
+            entry = cache_entry if self.own_kv else getattr(ctx, "state_entry", None)
+            if entry is None:
+                raise ValueError("a layer that borrows its keys and values needs a cache entry "
+                                 "for the state of its own convolution")
+            state = ctx.cache.state_view(entry).state
+        kernels.conv_rope_store(row, part, qkvg, nh, n_own, hd, hdv, taps, self.conv_w, cos, sin,
+                                rotary_dim, self.out_gate, state, 0, ctx,
+                                view if self.own_kv else None)
+        q = qkvg[:, :nh * hd]
+        out = ctx.new(T, nh * hdv)
+        if ctx.mode == PREFILL:
+            if self.own_kv:
+                k = qkvg[:, nh * hd:(nh + nkv) * hd]
+                v = qkvg[:, (nh + nkv) * hd:C]
+                ctx.step_kv[cache_entry] = (k, v, None)
+            else:
+                k, v, _ = ctx.step_kv[cache_entry]
+            kernels.attention_prefill(q, k, v, out, ctx, nh, nkv, hd, s.scale, window,
+                                      value_dim=hdv, sinks=self.sinks, dist_bias=self.dist_bias,
+                                      keep_first=self.keep_first)
+        else:
+            kernels.attention_decode(q, out, view, ctx, nh, nkv, hd, s.scale, window,
+                                     value_dim=hdv, sinks=self.sinks, dist_bias=self.dist_bias,
+                                     keep_first=self.keep_first)
+        if self.out_gate:
+            kernels.gate_sigmoid(out, qkvg[:, C:])
         return self.out.partial(out)
 
     def _attend_prompt(self, qkv: torch.Tensor, vt, ctx, cache_entry: int, writes_cache: bool,

@@ -7,6 +7,11 @@
 "post": the same without the two pre norms: a branch reads the stream itself.
 ``residual_mult`` m: every branch joins as h += m * (...).  A spec without a feed-forward
 gives a layer of the mixer branch alone (and no norms of the second branch).
+``token_side``: after the feed-forward (or, without one, after the mixer) the layer takes an
+input from the token itself: with e the layer's slice of the token's row of a table the
+layers share (``ctx.token_side_rows``), g = gelu_tanh(W_gate h) * e, y = W_proj g and
+h += y / rms(y) * w; tensors ``side.gate_proj.weight``, ``side.proj.weight``,
+``side.norm.weight``.
 
 The residual sum, the norm of the branch and the norm that feeds the next
 branch are one kernel launch, so a block receives its input already normed
@@ -19,8 +24,10 @@ from typing import Dict, Optional
 
 import torch
 
-from ..config.base import BlockSpec, IdentityNormSpec
+from .. import kernels
+from ..config.base import BlockSpec, IdentityNormSpec, NormSpec
 from .base import ParamSpec, feed_forward_class, mixer_class, norm_class, register_block
+from .linear import Linear
 from .norm import fused_residual
 
 
@@ -47,6 +54,17 @@ class Block:
         self.mixer = mixer_class(spec.mixer.kind)(spec.mixer, hidden_size, dtype, device)
         self.ffn = (feed_forward_class(spec.feed_forward.kind)(spec.feed_forward, hidden_size,
                                                                dtype, device) if has_ffn else None)
+        self.side = getattr(spec, "token_side", None)
+        self.side_gate: Optional[Linear] = None
+        self.side_proj: Optional[Linear] = None
+        self.side_in = self.side_norm = None
+        if self.side is not None:
+            if self.side.dim < 1 or self.side.offset < 0:
+                raise ValueError("a token input needs a positive width and an offset in its table")
+            # the gate reads the stream itself; the branch joins through a plain RMS norm
+            self.side_in = norm_class("identity")(IdentityNormSpec(), hidden_size, dtype, device)
+            self.side_norm = norm_class("rmsnorm")(
+                NormSpec(eps=self.side.eps, zero_centered=False), hidden_size, dtype, device)
 
     @classmethod
     def param_specs(cls, spec: BlockSpec, hidden_size: int) -> Dict[str, ParamSpec]:
@@ -67,6 +85,11 @@ class Block:
             F = feed_forward_class(spec.feed_forward.kind)
             for k, v in F.param_specs(spec.feed_forward, hidden_size).items():
                 out[f"ffn.{k}"] = v
+        side = getattr(spec, "token_side", None)
+        if side is not None:
+            out["side.gate_proj.weight"] = ParamSpec((side.dim, hidden_size))
+            out["side.proj.weight"] = ParamSpec((hidden_size, side.dim))
+            out["side.norm.weight"] = ParamSpec((hidden_size,), "norm")
         return out
 
     @property
@@ -76,6 +99,12 @@ class Block:
 
     def cache_request(self):
         return self.mixer.cache_request()
+
+    def state_request(self):
+        """The mixer's fixed-size state alone, for a call that reads another call's keys and
+        values and keeps state of its own in a cache entry of its own."""
+        ask = getattr(self.mixer, "state_request", None)
+        return ask() if ask is not None else None
 
     def load(self, tensors: Dict[str, torch.Tensor], dtype: torch.dtype,
              device: torch.device) -> None:
@@ -89,20 +118,44 @@ class Block:
         self.mixer.load(sub("mixer"), dtype, device)
         if self.ffn is not None:
             self.ffn.load(sub("ffn"), dtype, device)
+        if self.side is not None:
+            t = sub("side")
+            self.side_gate = Linear(t["gate_proj.weight"].to(device=device, dtype=dtype)
+                                    .contiguous(), role="token_side_gate")
+            self.side_proj = Linear(t["proj.weight"].to(device=device, dtype=dtype).contiguous(),
+                                    role="token_side_proj")
+            self.side_norm.load({"weight": t["norm.weight"]}, device)
+
+    def _token_side(self, xs: torch.Tensor, ctx) -> torch.Tensor:
+        """W_proj (gelu_tanh(W_gate xs) * e) for the stream xs [T, H] (rounded to the compute
+        dtype) and the tokens' slices e of the shared table."""
+        rows = getattr(ctx, "token_side_rows", None)
+        if rows is None:
+            raise ValueError("the layer takes a token input, but the model has no table for it")
+        sd = self.side
+        e = rows[:, sd.offset:sd.offset + sd.dim]
+        z = self.side_gate(xs, out_dtype=torch.float32)
+        g = ctx.new(xs.shape[0], sd.dim)
+        kernels.gelu_mul_rows(z, e, g)
+        return self.side_proj.partial(g)
 
     def forward(self, h: torch.Tensor, x: torch.Tensor, ctx, cache_entry: int,
                 writes_cache: bool, next_norm) -> Optional[torch.Tensor]:
         """h: [T, H] 32-bit stream (updated in place); x = pre_mixer_norm(h)."""
         y = self.mixer.forward(x, ctx, cache_entry, writes_cache)
-        if self.ffn is None:
-            x3 = ctx.new(*x.shape) if next_norm is not None else None
-            _join(h, y, self.post_mixer_norm, next_norm, x3, self.mult)
-            return x3
-        x2 = ctx.new(*x.shape)
-        _join(h, y, self.post_mixer_norm, self.pre_ffn_norm, x2, self.mult)
-        d = self.ffn.forward(x2, ctx)
+        post = self.post_mixer_norm
+        if self.ffn is not None:
+            x2 = ctx.new(*x.shape)
+            _join(h, y, post, self.pre_ffn_norm, x2, self.mult)
+            y = self.ffn.forward(x2, ctx)
+            post = self.post_ffn_norm
         x3 = ctx.new(*x.shape) if next_norm is not None else None
-        _join(h, d, self.post_ffn_norm, next_norm, x3, self.mult)
+        if self.side is None:
+            _join(h, y, post, next_norm, x3, self.mult)
+            return x3
+        xs = ctx.new(*x.shape)
+        _join(h, y, post, self.side_in, xs, self.mult)
+        _join(h, self._token_side(xs, ctx), self.side_norm, next_norm, x3)
         return x3
 
 

@@ -22,7 +22,11 @@ Options of the spec: a bias on the router's logits (``router_bias``); weights th
 softmax over the chosen experts' logits, the logits making the choice (``weighting``
 "softmax_top"); and a shared expert of the same form that every token uses, its output
 multiplied by sigmoid(w_sg . x), one number per token (``shared_size``): it is one more
-slice of the partial sums.
+slice of the partial sums; scores that are the softmax over all the router's outputs, with the
+chosen ones renormalised and multiplied by a constant (``weighting`` "softmax_all",
+``route_scale``); and identity experts (``n_identity``): router outputs beyond the experts
+that have no tensors and whose output is the input itself, times the weight.  A pair that
+chose one is left out of the plan, and a small kernel writes its row of the partial sums.
 """
 from __future__ import annotations
 
@@ -43,11 +47,16 @@ class RoutedFeedForward:
             raise ValueError("the experts must form equal groups")
         if not 1 <= spec.keep_groups <= spec.n_groups:
             raise ValueError("keep_groups must lie in 1..n_groups")
-        if spec.top > spec.keep_groups * (spec.n_experts // spec.n_groups):
+        if spec.top > spec.keep_groups * (spec.n_experts // spec.n_groups) + \
+                int(getattr(spec, "n_identity", 0) or 0):
             raise ValueError("top exceeds the experts of the groups kept")
         self.spec, self.hidden_size, self.dtype = spec, hidden_size, dtype
         self.weighting = getattr(spec, "weighting", "sigmoid")
-        if self.weighting not in ("sigmoid", "softmax_top"):
+        self.n_identity = int(getattr(spec, "n_identity", 0) or 0)
+        self.route_scale = float(getattr(spec, "route_scale", 1.0))
+        if self.n_identity < 0 or (self.n_identity and spec.n_groups != 1):
+            raise ValueError("identity experts go with ungrouped routing")
+        if self.weighting not in ("sigmoid", "softmax_top", "softmax_all"):
             raise ValueError(f"unknown expert weighting {self.weighting!r}")
         if self.weighting == "softmax_top" and spec.correction:
             raise ValueError("weights by softmax over the chosen logits go without a correction")
@@ -62,9 +71,10 @@ class RoutedFeedForward:
     @classmethod
     def param_specs(cls, spec: RoutedFeedForwardSpec, hidden_size: int) -> Dict[str, ParamSpec]:
         ff = spec.intermediate_size
-        p = {"router.weight": ParamSpec((spec.n_experts, hidden_size))}
+        n_out = spec.n_experts + int(getattr(spec, "n_identity", 0) or 0)
+        p = {"router.weight": ParamSpec((n_out, hidden_size))}
         if spec.correction:
-            p["router.correction"] = ParamSpec((spec.n_experts,), "float32")
+            p["router.correction"] = ParamSpec((n_out,), "float32")
         for e in range(spec.n_experts):
             p[f"experts.{e}.gate_proj.weight"] = ParamSpec((ff, hidden_size))
             p[f"experts.{e}.up_proj.weight"] = ParamSpec((ff, hidden_size))
@@ -109,7 +119,8 @@ class RoutedFeedForward:
         wts = torch.empty((T, s.top), dtype=torch.float32, device=x.device)
         kernels.moe_route(x, self.w_router, self.correction, s.n_groups, s.keep_groups, s.top,
                           ids, wts, bias=self.router_bias,
-                          softmax_top=self.weighting == "softmax_top")
+                          softmax_top=self.weighting == "softmax_top",
+                          softmax_all=self.weighting == "softmax_all", scale=self.route_scale)
         return ids, wts
 
     def _shared(self, x: torch.Tensor, out: torch.Tensor) -> None:
@@ -127,6 +138,8 @@ class RoutedFeedForward:
         y = torch.empty((s.top + n_sh, T, H), dtype=torch.float32, device=x.device)
         if n_sh:
             self._shared(x, y[s.top])
+        if self.n_identity:
+            kernels.moe_identity(x, ids, wts, s.n_experts, y[:s.top])
         if (kernels.moe_grouped_tc_supported(x, self.w_gate) and
                 kernels.moe_grouped_tc_supported(z, self.w_down)):
             # bfloat16 on the tensor cores: the tokens are brought into the plan's order

@@ -44,6 +44,20 @@ class RotaryEmbedding:
         f = [base ** (-2.0 * i / dims) / float(self.spec.factor) for i in range(dims // 2)]
         if sc is None:
             return f, 1.0
+        from ..config.base import BandScalingSpec
+        if isinstance(sc, BandScalingSpec):
+            # three bands of wavelength: kept, blended, divided by the factor
+            out = []
+            for fi in f:
+                wavelength = 2.0 * math.pi / fi
+                if wavelength < sc.original / sc.high:
+                    out.append(fi)
+                elif wavelength > sc.original / sc.low:
+                    out.append(fi / sc.factor)
+                else:
+                    t = (sc.original / wavelength - sc.low) / (sc.high - sc.low)
+                    out.append((1.0 - t) * fi / sc.factor + t * fi)
+            return out, 1.0
 
         def pair_of(turns: float) -> float:
             return dims * math.log(sc.original / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
