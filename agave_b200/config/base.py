@@ -177,6 +177,9 @@ class AttentionSpec:
     # the concatenated heads are multiplied element by element by sigmoid(W_g x) (tensor
     # ``g_proj.weight``) before the output projection
     out_gate: bool = False
+    # the cache keeps every key of this layer whatever its own mask: another call reads the
+    # entry through a mask that reaches further back
+    keep_all_keys: bool = False
 
     @property
     def v_dim(self) -> int:

@@ -317,9 +317,13 @@ class KadavikConfig:
                 sc = BandScalingSpec(factor=factor, original=original, low=low, high=high)
             position = RotarySpec(theta=m.rot.base, factor=1.0,
                                   rotary_dim=0 if m.rot.dims == m.dim else m.rot.dims, scaling=sc)
+        # the layers that borrow this one's keys and values may look further back than it does
+        readers = [l.mixer for l in self.layers if l.mixer.kv_from == i]
+        wider = any((r.window, r.keep_first if r.window is not None else 0) !=
+                    (m.window, m.keep_first if m.window is not None else 0) for r in readers)
         return AttentionSpec(
             n_heads=m.heads, n_kv_heads=m.kv_heads, head_dim=m.dim, scale=m.scale,
-            window=m.window, qk_norm=None, position=position,
+            window=m.window, qk_norm=None, position=position, keep_all_keys=wider,
             value_dim=0 if m.vdim == m.dim else m.vdim, own_kv=m.kv_from is None,
             keep_first=m.keep_first if m.window is not None else 0,
             # (a layer of this design always runs the row kernel of the convolution: one tap

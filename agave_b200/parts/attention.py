@@ -175,7 +175,7 @@ class AttentionMixer:
         # (a mask of blocks needs the keys of one block: a ring of that many rows; a window
         # behind which the first keys stay visible keeps every key)
         window = self.chunk if self.chunk is not None else self.spec.window
-        if self.keep_first:
+        if self.keep_first or getattr(self.spec, "keep_all_keys", False):
             window = None
         kv = KVRequest(self.spec.n_kv_heads, self.spec.head_dim, window,
                        0 if self.value_dim == self.spec.head_dim else self.value_dim)

@@ -89,7 +89,7 @@ def attention_keys_values(h, m: dict, w: Dict[str, torch.Tensor], p: str):
     """(keys as a cache would hold them [T, G, dim], values [T, G, vdim]) of the layer whose
     tensors start with ``p``."""
     T = h.shape[0]
-    G = m["kv_heads"]
+    G = m.get("kv_heads", m["heads"])
     k = causal_conv(h @ w[p + "k"].to(F).T, w[p + "k.conv"].to(F)) if m.get("conv") else \
         h @ w[p + "k"].to(F).T
     v = causal_conv(h @ w[p + "v"].to(F).T, w[p + "v.conv"].to(F)) if m.get("conv") else \
@@ -103,7 +103,7 @@ def attention_keys_values(h, m: dict, w: Dict[str, torch.Tensor], p: str):
 def attention_mixer(h, m: dict, w: Dict[str, torch.Tensor], p: str, k, v):
     """h [T, width] of one sequence from position 0; k, v: this layer's own or another's."""
     T = h.shape[0]
-    H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    H, G, d, dv = m["heads"], m.get("kv_heads", m["heads"]), m["dim"], m["vdim"]
     q = h @ w[p + "q"].to(F).T
     if m.get("conv"):
         q = causal_conv(q, w[p + "q.conv"].to(F))
@@ -112,7 +112,7 @@ def attention_mixer(h, m: dict, w: Dict[str, torch.Tensor], p: str, k, v):
         q = rotate(q, torch.arange(T), m["rot"])
     mask = m.get("mask")
     size = mask["size"] if mask is not None else None
-    keep = mask.get("keep_first", 0) if mask is not None else 0
+    keep = (mask.get("keep_first") or 0) if mask is not None else 0
     see = torch.tensor([[visible(i, j, size, keep) for j in range(T)] for i in range(T)])
     out = torch.zeros(T, H, dv, dtype=F)
     for a in range(H):
@@ -165,7 +165,7 @@ def route(h, f: dict, w, p: str):
     choice = s + w[p + "correction"].to(F)
     idx = torch.topk(choice, r["top"], dim=-1).indices
     sc = torch.gather(s, 1, idx)
-    return idx, sc / (sc.sum(-1, keepdim=True) + 1e-20) * r["scale"]
+    return idx, sc / (sc.sum(-1, keepdim=True) + 1e-20) * r.get("scale", 1.0)
 
 
 def moe(h, f: dict, w, p: str, chosen=None):
@@ -175,7 +175,7 @@ def moe(h, f: dict, w, p: str, chosen=None):
         idx = chosen
         s = torch.softmax(h @ w[p + "router"].to(F).T, -1)
         sc = torch.gather(s, 1, idx)
-        wt = sc / (sc.sum(-1, keepdim=True) + 1e-20) * r["scale"]
+        wt = sc / (sc.sum(-1, keepdim=True) + 1e-20) * r.get("scale", 1.0)
     y = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for c in range(idx.shape[1]):
@@ -205,7 +205,7 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens, chosen=None, layers_o
     router's own choice."""
     tokens = torch.as_tensor(tokens, dtype=torch.long)
     eps = cfg["norm"]["eps"]
-    x = w["embed"].to(F)[tokens] * cfg["embedding"]["scale"]
+    x = w["embed"].to(F)[tokens] * (cfg.get("embedding") or {}).get("scale", 1.0)
     kv = {}
     for i, layer in enumerate(cfg["layers"]):
         p = f"l{i}."
@@ -233,4 +233,4 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens, chosen=None, layers_o
         if layers_out is not None:
             layers_out.append(x.clone())
     x = rms_norm(x, w["final.norm"].to(F), eps)
-    return x @ w["embed"].to(F).T * cfg["logit_scale"]
+    return x @ w["embed"].to(F).T * cfg.get("logit_scale", 1.0)
