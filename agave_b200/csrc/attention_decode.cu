@@ -91,7 +91,20 @@ struct DecodeArgs {
     const float* sinks;        // [nh] sink logits (exp(sink) joins the denominator once), or null
     const float* dist_bias;    // [nh, n_dist] added to the scaled score by distance, or null
     int n_dist;
+    // With a sliding window, the sequence's first keep_first keys stay visible behind it.  The
+    // walk over the keys then starts min(keep_first, window start) places before the window:
+    // those places stand for the first keys (see walked_key).  Copied tiles only.
+    int keep_first = 0;
 };
+
+// The walk's first place for a query at position p whose window starts at lo_w, and the key a
+// place of the walk stands for: the places before the window are the kept first keys.
+__device__ __forceinline__ int walk_start(const DecodeArgs& a, int lo_w) {
+    return lo_w - min(a.keep_first, lo_w);
+}
+__device__ __forceinline__ int walked_key(int place, int lo, int lo_w) {
+    return place < lo_w ? place - lo : place;
+}
 
 // The learned bias of head h for the key at position j seen from position p.
 __device__ __forceinline__ float distance_bias(const DecodeArgs& a, int p, int j, int h) {
@@ -244,7 +257,8 @@ attention_decode_split_kernel(DecodeArgs a) {
         return;
     }
     const int p = a.positions[b];
-    const int lo = first_visible(p, a.window);
+    const int lo_w = first_visible(p, a.window);
+    const int lo = walk_start(a, lo_w);
     const int j0 = lo + split * a.chunk;
     if (j0 > p) return;
     const int n = min(a.chunk, p - j0 + 1);                   // keys of this chunk
@@ -260,7 +274,7 @@ attention_decode_split_kernel(DecodeArgs a) {
     // ---- where each key row of the chunk lives (one page-table read per row)
     const int* table = a.page_table + (size_t)slot * a.max_pages;
     for (int r = tid; r < n; r += AD_THREADS) {
-        const int row = (j0 + r) % a.cap;
+        const int row = walked_key(j0 + r, lo, lo_w) % a.cap;
         rowoff[r] = table[row / a.page] * a.page + row % a.page;
     }
     // ---- the group's queries, 32-bit
@@ -610,7 +624,8 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq,
         return;
     }
     const int p = a.positions[b];
-    const int lo = first_visible(p, a.window);
+    const int lo_w = first_visible(p, a.window);
+    const int lo = TMA ? lo_w : walk_start(a, lo_w);
     // Tiles this sequence has: from its first key on, or (TMA) the cache pages it touches.
     // A full window in a ring of its own size is the ring's pages, every row of them: the
     // tiles are then counted in ring rows (tile k is the ring's page k), which saves the
@@ -636,7 +651,7 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq,
     // cache row of key (first + tid), or -1 beyond position p
     auto row_of = [&](int first) {
         const int key = first + tid;
-        const int row = key % a.cap;
+        const int row = walked_key(key, lo, lo_w) % a.cap;
         return key <= p ? table[row / a.page] * a.page + row % a.page : -1;
     };
     if (!TMA && has && tid < DM_KEYS) {
@@ -660,6 +675,16 @@ attention_decode_mma_kernel(DecodeArgs a, int cs, FuseQK fq,
     // cache row of this thread's key of the next tile, or -1 beyond position p
     auto next_lookup = [&]() {
         int r = -1;
+        if (lo != lo_w) {
+            // (kept first keys: the place's key is looked up directly; the cache keeps every
+            // key then, so a key's ring place is the key)
+            if (look_key <= p) {
+                const int row = walked_key(look_key, lo, lo_w) % a.cap;
+                r = table[row / a.page] * a.page + row % a.page;
+            }
+            look_key += W * DM_KEYS;
+            return r;
+        }
         if (look_key <= p)
             r = pshift >= 0 ? (table[look_ring >> pshift] << pshift) + (look_ring & (a.page - 1))
                             : table[look_ring / a.page] * a.page + look_ring % a.page;
@@ -1240,8 +1265,9 @@ int launch_decode_form(const DecodeArgs& a, int B, cudaStream_t stream, const Fu
     // 64 sequences with a ring of 512 12.5 -> 11.2; but one tile per CTA (8 sequences with
     // a ring of 512) 5.7 -> 6.1, which stays with the copies.
     // (a distance bias wants every key's position, which the ring-counted TMA tiles do not give)
-    bool tma = can && form == 2 && !a.dist_bias;
-    if (can && form == 0 && !a.dist_bias) {
+    // (nor do they know kept first keys)
+    bool tma = can && form == 2 && !a.dist_bias && !a.keep_first;
+    if (can && form == 0 && !a.dist_bias && !a.keep_first) {
         const int G = a.nh / a.nkv, groups = a.nkv * ((G + DM_HEADS - 1) / DM_HEADS);
         int cs, clusters;
         const int most = most_tiles(a, true);
@@ -1295,8 +1321,11 @@ static int attention_decode_impl(const void* q, long long q_stride, void* out, i
                                  int max_keys, float* part_acc, float* part_ml, int* counters,
                                  cudaStream_t stream, const FuseQK& fq,
                                  const float* sinks = nullptr, const float* dist_bias = nullptr,
-                                 int n_dist = 0) {
+                                 int n_dist = 0, int keep_first = 0) {
     AGV_REQUIRE(B >= 0 && nh > 0 && nkv > 0 && hd > 0, "attention_decode: bad sizes");
+    AGV_REQUIRE(keep_first >= 0 && (keep_first == 0 || (window > 0 && !dist_bias && !fq.part)),
+                "attention_decode: kept first keys go with a sliding window, without a distance "
+                "bias, and with finished queries");
     AGV_REQUIRE(!dist_bias || (n_dist > 0 && !fq.part), "attention_decode: a distance bias needs "
                 "its table and finished queries");
     AGV_REQUIRE(!fq.q_only || !fq.store_kv, "attention_decode: queries alone bring nothing to store");
@@ -1324,7 +1353,7 @@ static int attention_decode_impl(const void* q, long long q_stride, void* out, i
                 smem);
     DecodeArgs a{q, q_stride, out, k_pool, v_pool, page_table, slots, positions, part_acc, part_ml,
                  counters, max_pages, page, cap, nh, nkv, hd, window, n_splits, ch, scale, sinks,
-                 dist_bias, n_dist};
+                 dist_bias, n_dist, keep_first};
     if (dtype == AGV_BF16 && hd % 8 == 0 && hd <= 256 && ch == DM_KEYS &&
         (fq.part || (q_stride % 8 == 0 && agv_aligned(q, 16)))) {
         if (hd <= 64) return launch_decode_form<64>(a, B, stream, fq);
@@ -1393,6 +1422,22 @@ AGV_API int agv_attention_decode_ex2(const void* q, long long q_stride, void* ou
                                  positions, max_pages, page, cap, B, nh, nkv, hd, scale, window,
                                  max_keys, part_acc, part_ml, counters, stream, FuseQK{}, sinks,
                                  dist_bias, n_dist);
+}
+
+// The same with kept first keys: position p also sees the keys j < keep_first behind its
+// window.  max_keys then counts them: at least position - window start + 1 + min(keep_first,
+// window start) of every entry.  The cache entry must keep every key (cap above every position).
+AGV_API int agv_attention_decode_ex3(const void* q, long long q_stride, void* out, int dtype,
+                                     const void* k_pool, const void* v_pool, const int* page_table,
+                                     const int* slots, const int* positions, int max_pages, int page,
+                                     int cap, int B, int nh, int nkv, int hd, float scale, int window,
+                                     int max_keys, float* part_acc, float* part_ml, int* counters,
+                                     const float* sinks, const float* dist_bias, int n_dist,
+                                     int keep_first, cudaStream_t stream) {
+    return attention_decode_impl(q, q_stride, out, dtype, k_pool, v_pool, page_table, slots,
+                                 positions, max_pages, page, cap, B, nh, nkv, hd, scale, window,
+                                 max_keys, part_acc, part_ml, counters, stream, FuseQK{}, sinks,
+                                 dist_bias, n_dist, keep_first);
 }
 
 // Whether agv_attention_decode_fused takes these sizes: bfloat16, head sizes 64, 128,

@@ -85,7 +85,7 @@ attention_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_st
                              __nv_bfloat16* __restrict__ out, const int* __restrict__ cu_seqlens,
                              int nh, int nkv, int hd, float scale_log2e, int window,
                              const float* __restrict__ sinks, int hdv, long long v_stride,
-                             const float* __restrict__ dist_bias, int n_dist) {
+                             const float* __restrict__ dist_bias, int n_dist, int keep_first) {
     pdl_wait();
     pdl_launch_next();
     constexpr int FA_M = NW * 16, FA_THREADS = NW * 32;
@@ -111,11 +111,16 @@ attention_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_st
     const int j_hi = min(m0 + FA_M - 1, len - 1);
     const int j_lo = first_visible(m0, window);
     const int t_lo = j_lo / FA_N, t_hi = j_hi / FA_N;
+    // the tiles walked: those of the kept first keys that lie wholly before the window's
+    // first tile, then the window's
+    const int n_kept = keep_first > 0 ? min((keep_first + FA_N - 1) / FA_N, t_lo) : 0;
+    const int n_walk = t_hi - t_lo + 1 + n_kept;
+    auto tile_of = [&](int i) { return i < n_kept ? i : t_lo + (i - n_kept); };
 
     load_tile<HDP, FA_M, FA_THREADS>(Qs, qb, q_stride, m0, len, hd);
-    load_tile<HDP, FA_N, FA_THREADS>(Ks, kb, kv_stride, t_lo * FA_N, len, hd);
+    load_tile<HDP, FA_N, FA_THREADS>(Ks, kb, kv_stride, tile_of(0) * FA_N, len, hd);
     cp_commit();
-    load_tile<HDP, FA_N, FA_THREADS>(Vs, vb, v_stride, t_lo * FA_N, len, hdv);
+    load_tile<HDP, FA_N, FA_THREADS>(Vs, vb, v_stride, tile_of(0) * FA_N, len, hdv);
     cp_commit();
 
     float o[HDP / 8][4];
@@ -124,7 +129,8 @@ attention_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_st
     float row_m[2] = {-INFINITY, -INFINITY}, row_l[2] = {0.f, 0.f};
     const int qrow = m0 + warp * 16 + gid;             // this thread's rows: qrow, qrow + 8
 
-    for (int t = t_lo; t <= t_hi; ++t) {
+    for (int it = 0; it < n_walk; ++it) {
+        const int t = tile_of(it);
         cp_wait<1>();                                   // K (and Q) of this tile have landed
         __syncthreads();
         // ---- S = Q K^T for 16 rows x 64 keys
@@ -146,7 +152,8 @@ attention_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_st
             }
         }
         __syncthreads();                                // every warp is done with this K tile
-        if (t < t_hi) load_tile<HDP, FA_N, FA_THREADS>(Ks, kb, kv_stride, (t + 1) * FA_N, len, hd);
+        if (it + 1 < n_walk)
+            load_tile<HDP, FA_N, FA_THREADS>(Ks, kb, kv_stride, tile_of(it + 1) * FA_N, len, hd);
         cp_commit();
         // ---- bounds, running maximum and sum
         const int j0 = t * FA_N;
@@ -157,7 +164,8 @@ attention_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_st
             for (int e = 0; e < 4; ++e) {
                 const int j = j0 + i * 8 + tig * 2 + (e & 1);
                 const int p = qrow + (e >> 1) * 8;
-                const bool ok = j <= p && j < len && j >= first_visible(p, window);
+                const bool ok = j <= p && j < len &&
+                                (j >= first_visible(p, window) || j < keep_first);
                 float val = -INFINITY;
                 if (ok) {
                     val = s[i][e] * scale_log2e;
@@ -210,7 +218,8 @@ attention_prefill_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_st
             }
         }
         __syncthreads();                                // every warp is done with this V tile
-        if (t < t_hi) load_tile<HDP, FA_N, FA_THREADS>(Vs, vb, v_stride, (t + 1) * FA_N, len, hdv);
+        if (it + 1 < n_walk)
+            load_tile<HDP, FA_N, FA_THREADS>(Vs, vb, v_stride, tile_of(it + 1) * FA_N, len, hdv);
         cp_commit();
     }
     // ---- normalise and store
@@ -247,7 +256,7 @@ template <int HDP, int NW>
 int launch_fa(const void* q, long long q_stride, const void* k, const void* v, long long kv_stride,
               void* out, const int* cu_seqlens, int B, int max_len, int nh, int nkv, int hd,
               float scale, int window, cudaStream_t stream, const float* sinks, int hdv,
-              long long v_stride, const float* dist_bias, int n_dist) {
+              long long v_stride, const float* dist_bias, int n_dist, int keep_first) {
     auto kern = attention_prefill_mma_kernel<HDP, NW>;
     constexpr int FA_M = NW * 16, FA_THREADS = NW * 32;
     constexpr int smem = (FA_M + 2 * FA_N) * HDP * 2;
@@ -259,7 +268,7 @@ int launch_fa(const void* q, long long q_stride, const void* k, const void* v, l
     dim3 grid((max_len + FA_M - 1) / FA_M, nh, B);
     agv_launch(kern, grid, FA_THREADS, smem, stream, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v,
         kv_stride, (__nv_bfloat16*)out, cu_seqlens, nh, nkv, hd,
-        scale * 1.4426950408889634f, window, sinks, hdv, v_stride, dist_bias, n_dist);
+        scale * 1.4426950408889634f, window, sinks, hdv, v_stride, dist_bias, n_dist, keep_first);
     AGV_LAUNCH_OK("attention_prefill_mma_kernel");
     return 0;
 }
@@ -280,12 +289,33 @@ AGV_API int agv_attention_prefill_mma_supported(int hd, long long q_stride, long
 // hdv / v_stride: the value head size and the value rows' stride where they differ from the
 // keys' (out is then [T, nh * hdv]); dist_bias [nh, n_dist]: added to the scaled score of a key
 // at distance min(t - j, n_dist - 1), or null.
+AGV_API int agv_attention_prefill_mma_ex3(const void* q, long long q_stride, const void* k,
+                                          const void* v, long long kv_stride, void* out,
+                                          const int* cu_seqlens, int B, int max_len, int nh, int nkv,
+                                          int hd, float scale, int window, const float* sinks,
+                                          int hdv, long long v_stride, const float* dist_bias,
+                                          int n_dist, int keep_first, cudaStream_t stream);
+
 AGV_API int agv_attention_prefill_mma_ex2(const void* q, long long q_stride, const void* k,
                                           const void* v, long long kv_stride, void* out,
                                           const int* cu_seqlens, int B, int max_len, int nh, int nkv,
                                           int hd, float scale, int window, const float* sinks,
                                           int hdv, long long v_stride, const float* dist_bias,
                                           int n_dist, cudaStream_t stream) {
+    return agv_attention_prefill_mma_ex3(q, q_stride, k, v, kv_stride, out, cu_seqlens, B, max_len,
+                                         nh, nkv, hd, scale, window, sinks, hdv, v_stride,
+                                         dist_bias, n_dist, 0, stream);
+}
+
+// keep_first: with a sliding window, position p also sees the keys j < keep_first.
+AGV_API int agv_attention_prefill_mma_ex3(const void* q, long long q_stride, const void* k,
+                                          const void* v, long long kv_stride, void* out,
+                                          const int* cu_seqlens, int B, int max_len, int nh, int nkv,
+                                          int hd, float scale, int window, const float* sinks,
+                                          int hdv, long long v_stride, const float* dist_bias,
+                                          int n_dist, int keep_first, cudaStream_t stream) {
+    AGV_REQUIRE(keep_first >= 0 && (keep_first == 0 || window > 0),
+                "attention: kept first keys go with a sliding window");
     AGV_REQUIRE(B >= 0 && nh > 0 && nkv > 0 && hd > 0 && max_len >= 0, "attention: bad sizes");
     AGV_REQUIRE(hdv > 0 && hdv % 8 == 0 && hdv <= 256 && v_stride % 8 == 0,
                 "attention: the value head size (%d) must be a multiple of 8 up to 256", hdv);
@@ -304,10 +334,10 @@ AGV_API int agv_attention_prefill_mma_ex2(const void* q, long long q_stride, con
 #define AGV_FA(HDP)                                                                             \
     return wide ? launch_fa<HDP, 8>(q, q_stride, k, v, kv_stride, out, cu_seqlens, B, max_len,  \
                                     nh, nkv, hd, scale, window, stream, sinks, hdv, v_stride,    \
-                                    dist_bias, n_dist)                                           \
+                                    dist_bias, n_dist, keep_first)                               \
                 : launch_fa<HDP, 4>(q, q_stride, k, v, kv_stride, out, cu_seqlens, B, max_len,  \
                                     nh, nkv, hd, scale, window, stream, sinks, hdv, v_stride,    \
-                                    dist_bias, n_dist)
+                                    dist_bias, n_dist, keep_first)
     const int widest = hd > hdv ? hd : hdv;
     if (widest <= 64) AGV_FA(64);
     if (widest <= 128) AGV_FA(128);

@@ -54,6 +54,7 @@ struct AtArgs {
     const int* cu;                 // [B + 1]
     int nh, nkv, hd, G, QT;        // G heads packed per CTA, QT = 128 / G tokens
     int window;
+    int keep_first;                // with a window: the first keys that stay visible behind it
     float scale_log2e;
     int kb;                        // 64-element blocks of head_dim
     int tmem_cols;
@@ -163,7 +164,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
     // visible key range of this query tile: causal end, window start
     const int j_hi = min(q0 + a.QT - 1, len - 1);
     const int j_lo = first_visible(q0, a.window);
-    const int t_lo = j_lo / AT_N, n_tiles = j_hi / AT_N - t_lo + 1;
+    // the tiles walked: those of the kept first keys that lie wholly before the window's
+    // first tile, then the window's
+    const int t_lo = j_lo / AT_N;
+    const int n_kept = a.keep_first > 0 ? min((a.keep_first + AT_N - 1) / AT_N, t_lo) : 0;
+    const int n_tiles = j_hi / AT_N - t_lo + 1 + n_kept;
+    auto tile_of = [&](int j) { return j < n_kept ? j : t_lo + (j - n_kept); };
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
@@ -215,7 +221,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
             mbar_expect_tx(&k_full[s], (uint32_t)k_bytes);
             for (int kb = 0; kb < a.kb; ++kb)
                 tma_load_3d(Ks + s * k_bytes + kb * (AT_N * 128), &map_k, kb * 64, kvh,
-                            seq0 + (t_lo + j) * AT_N, &k_full[s]);
+                            seq0 + tile_of(j) * AT_N, &k_full[s]);
             return true;
         };
         auto load_v = [&](int j) -> bool {
@@ -225,7 +231,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                 return false;
             }
             mbar_expect_tx(&v_full[s], (uint32_t)v_bytes);
-            tma_load_2d(Vs + s * v_stage, &map_vt, vt0 + (t_lo + j) * AT_N, kvh * a.hd, &v_full[s]);
+            tma_load_2d(Vs + s * v_stage, &map_vt, vt0 + tile_of(j) * AT_N, kvh * a.hd, &v_full[s]);
             return true;
         };
         // keys run one tile ahead of values: K of tile j + 1 is wanted before V of tile j
@@ -334,9 +340,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&s_free[s]);
-            const int j0 = (t_lo + j) * AT_N;
+            const int j0 = tile_of(j) * AT_N;
             // a tile every row of the CTA sees whole needs no bounds
-            const bool whole = j0 + AT_N - 1 <= q_min && j0 >= first_visible(q_max, a.window);
+            const bool whole = j0 + AT_N - 1 <= q_min &&
+                               (j0 >= first_visible(q_max, a.window) || j0 + AT_N <= a.keep_first);
             float sv[64];
             if (whole) {
 #pragma unroll
@@ -346,7 +353,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
 #pragma unroll
                 for (int c = 0; c < 64; ++c) {
                     const int key = j0 + c;
-                    sv[c] = (key <= qp && key > lo) ? __uint_as_float(sr[c >> 4][c & 15]) : -INFINITY;
+                    sv[c] = (key <= qp && (key > lo || key < a.keep_first))
+                                ? __uint_as_float(sr[c >> 4][c & 15]) : -INFINITY;
                 }
             }
             if (BIAS) {
@@ -576,6 +584,13 @@ AGV_API int agv_attention_prefill_tc_ex2(const void* q, long long q_stride, cons
                                          int window, const float* sinks, const float* dist_bias,
                                          int n_dist, cudaStream_t stream);
 
+AGV_API int agv_attention_prefill_tc_ex3(const void* q, long long q_stride, const void* k,
+                                         const void* v, long long kv_stride, void* out, void* vt,
+                                         long long vt_cols, int vt_ready, const int* cu_seqlens, int B,
+                                         int T, int max_len, int nh, int nkv, int hd, float scale,
+                                         int window, const float* sinks, const float* dist_bias,
+                                         int n_dist, int keep_first, cudaStream_t stream);
+
 AGV_API int agv_attention_prefill_tc_ex(const void* q, long long q_stride, const void* k,
                                         const void* v, long long kv_stride, void* out, void* vt,
                                         long long vt_cols, int vt_ready, const int* cu_seqlens, int B,
@@ -594,7 +609,22 @@ AGV_API int agv_attention_prefill_tc_ex2(const void* q, long long q_stride, cons
                                          int T, int max_len, int nh, int nkv, int hd, float scale,
                                          int window, const float* sinks, const float* dist_bias,
                                          int n_dist, cudaStream_t stream) {
+    return agv_attention_prefill_tc_ex3(q, q_stride, k, v, kv_stride, out, vt, vt_cols, vt_ready,
+                                        cu_seqlens, B, T, max_len, nh, nkv, hd, scale, window, sinks,
+                                        dist_bias, n_dist, 0, stream);
+}
+
+// The same with kept first keys: with a sliding window, position p also sees the keys
+// j < keep_first.
+AGV_API int agv_attention_prefill_tc_ex3(const void* q, long long q_stride, const void* k,
+                                         const void* v, long long kv_stride, void* out, void* vt,
+                                         long long vt_cols, int vt_ready, const int* cu_seqlens, int B,
+                                         int T, int max_len, int nh, int nkv, int hd, float scale,
+                                         int window, const float* sinks, const float* dist_bias,
+                                         int n_dist, int keep_first, cudaStream_t stream) {
     AGV_REQUIRE(scale > 0.f, "attention: the tcgen05 kernel takes a positive score scale");
+    AGV_REQUIRE(keep_first >= 0 && (keep_first == 0 || window > 0),
+                "attention: kept first keys go with a sliding window");
     AGV_REQUIRE(!dist_bias || n_dist > 0, "attention: an empty distance table");
     AGV_REQUIRE(B >= 0 && T >= 0 && nh > 0 && nkv > 0 && hd > 0 && max_len >= 0,
                 "attention: bad sizes");
@@ -618,6 +648,7 @@ AGV_API int agv_attention_prefill_tc_ex2(const void* q, long long q_stride, cons
     a.G = packed_heads(nh, nkv);
     a.QT = AT_M / a.G;
     a.window = window;
+    a.keep_first = keep_first;
     a.scale_log2e = scale * 1.4426950408889634f;
     a.kb = (hd + 63) / 64;
     a.tmem_cols = AT_O_COL + hd <= 256 ? 256 : 512;

@@ -1334,7 +1334,7 @@ def attention_prefill_mma(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out
                           cu_seqlens: torch.Tensor, max_len: int, n_heads: int, n_kv_heads: int,
                           head_dim: int, scale: float, window: int,
                           sinks: Optional[torch.Tensor] = None, value_dim: int = 0,
-                          dist_bias: Optional[torch.Tensor] = None) -> None:
+                          dist_bias: Optional[torch.Tensor] = None, keep_first: int = 0) -> None:
     """Prompts that start at 0 on the tensor cores (bfloat16, head sizes in steps
     of 8 up to 256); q, k, v are row-strided views, out is dense.  ``value_dim``: the value
     head size where it differs from the keys'; ``dist_bias`` [nh, n]: see
@@ -1346,12 +1346,12 @@ def attention_prefill_mma(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out
     if dist_bias is not None:
         _dense(dist_bias, "dist_bias")
         assert dist_bias.dim() == 2 and dist_bias.shape[0] == n_heads
-    _check(library().agv_attention_prefill_mma_ex2(
+    _check(library().agv_attention_prefill_mma_ex3(
         _ptr(q), ctypes.c_longlong(q.stride(0)), _ptr(k), _ptr(v),
         ctypes.c_longlong(k.stride(0)), _ptr(out), _ptr(cu_seqlens), cu_seqlens.numel() - 1,
         max_len, n_heads, n_kv_heads, head_dim, ctypes.c_float(scale), window, _ptr(sinks),
         value_dim or head_dim, ctypes.c_longlong(v.stride(0)), _ptr(dist_bias),
-        dist_bias.shape[1] if dist_bias is not None else 0, _stream()))
+        dist_bias.shape[1] if dist_bias is not None else 0, int(keep_first), _stream()))
 
 
 def prefill_values_scratch(T: int, B: int, n_kv_heads: int, head_dim: int,
@@ -1378,7 +1378,7 @@ def attention_prefill_tc(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out:
                          head_dim: int, scale: float, window: int,
                          vt: Optional[torch.Tensor] = None,
                          sinks: Optional[torch.Tensor] = None,
-                         dist_bias: Optional[torch.Tensor] = None) -> None:
+                         dist_bias: Optional[torch.Tensor] = None, keep_first: int = 0) -> None:
     """Prompts that start at 0 on the tcgen05 tensor cores (bfloat16, head sizes in
     steps of 16 up to 256); q, k, v are row-strided views, out is dense.  ``vt``:
     the values already transposed (by ``qk_norm_rope_store``); else this call
@@ -1396,12 +1396,12 @@ def attention_prefill_tc(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out:
     if dist_bias is not None:
         _dense(dist_bias, "dist_bias")
         assert dist_bias.dim() == 2 and dist_bias.shape[0] == n_heads
-    _check(library().agv_attention_prefill_tc_ex2(
+    _check(library().agv_attention_prefill_tc_ex3(
         _ptr(q), ctypes.c_longlong(q.stride(0)), _ptr(k), _ptr(v),
         ctypes.c_longlong(k.stride(0)), _ptr(out), _ptr(vt), ctypes.c_longlong(vt.shape[1]),
         1 if ready else 0, _ptr(cu_seqlens), B, T, max_len, n_heads, n_kv_heads, head_dim,
         ctypes.c_float(scale), window, _ptr(sinks), _ptr(dist_bias),
-        dist_bias.shape[1] if dist_bias is not None else 0, _stream()))
+        dist_bias.shape[1] if dist_bias is not None else 0, int(keep_first), _stream()))
 
 
 def attention_tc_status() -> int:
@@ -1443,22 +1443,19 @@ def attention_prefill(q, k, v, out, ctx, n_heads, n_kv_heads, head_dim, scale, w
     if not window:
         keep_first = 0                    # (without a window every key is visible anyway)
     with _span(op, *_attention_cost(ctx, q, k, v, out, n_heads, head_dim, window)):
-        if keep_first:
-            attention_prefill_simt(q, k, v, out, ctx.positions, ctx.seq_index, ctx.cu_seqlens,
-                                   n_heads, n_kv_heads, head_dim, scale, window, value_dim=hdv,
-                                   sinks=sinks, dist_bias=dist_bias, keep_first=keep_first)
-        elif (aligned and same and head_dim % 16 == 0 and _PREFILL_TC and scale > 0 and
+        if (aligned and same and head_dim % 16 == 0 and _PREFILL_TC and scale > 0 and
                 q.shape[0] > PREFILL_TC_MIN_TOKENS):
             attention_prefill_tc(q, k, v, out, ctx.cu_seqlens, ctx.max_new, n_heads, n_kv_heads,
-                                 head_dim, scale, window, vt=vt, sinks=sinks, dist_bias=dist_bias)
+                                 head_dim, scale, window, vt=vt, sinks=sinks, dist_bias=dist_bias,
+                                 keep_first=keep_first)
         elif aligned and head_dim % 8 == 0 and hdv % 8 == 0:
             attention_prefill_mma(q, k, v, out, ctx.cu_seqlens, ctx.max_new, n_heads,
                                   n_kv_heads, head_dim, scale, window, sinks=sinks,
-                                  value_dim=hdv, dist_bias=dist_bias)
+                                  value_dim=hdv, dist_bias=dist_bias, keep_first=keep_first)
         else:
             attention_prefill_simt(q, k, v, out, ctx.positions, ctx.seq_index, ctx.cu_seqlens,
                                    n_heads, n_kv_heads, head_dim, scale, window, value_dim=hdv,
-                                   sinks=sinks, dist_bias=dist_bias)
+                                   sinks=sinks, dist_bias=dist_bias, keep_first=keep_first)
 
 
 def _attention_cost(ctx, q, k, v, out, n_heads, head_dim, window, n_kv_heads=0):
@@ -1540,7 +1537,7 @@ def attention_decode_split(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Ten
                            max_keys: int, part_acc: Optional[torch.Tensor] = None,
                            part_ml: Optional[torch.Tensor] = None,
                            sinks: Optional[torch.Tensor] = None,
-                           dist_bias: Optional[torch.Tensor] = None) -> None:
+                           dist_bias: Optional[torch.Tensor] = None, keep_first: int = 0) -> None:
     """One query per batch entry against the paged cache, keys split into chunks
     whose partial results go through scratch memory (allocated here if not given)."""
     B = q.shape[0]
@@ -1562,12 +1559,12 @@ def attention_decode_split(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Ten
     if dist_bias is not None:
         _dense(dist_bias, "dist_bias")
         assert dist_bias.dim() == 2 and dist_bias.shape[0] == n_heads
-    _check(library().agv_attention_decode_ex2(
+    _check(library().agv_attention_decode_ex3(
         _ptr(q), ctypes.c_longlong(q.stride(0)), _ptr(out), dtype_code(q.dtype), _ptr(k_pool),
         _ptr(v_pool), _ptr(page_table), _ptr(slots), _ptr(positions), page_table.shape[1], page,
         cap, B, n_heads, n_kv_heads, head_dim, ctypes.c_float(scale), window, max_keys,
         _ptr(part_acc), _ptr(part_ml), _ptr(counters), _ptr(sinks), _ptr(dist_bias),
-        dist_bias.shape[1] if dist_bias is not None else 0, _stream()))
+        dist_bias.shape[1] if dist_bias is not None else 0, int(keep_first), _stream()))
 
 
 _FUSED_DECODE = os.environ.get("AGAVE_B200_FUSED_DECODE_ATTENTION", "1") != "0"
@@ -1635,12 +1632,13 @@ def attention_decode(q, out, view, ctx, n_heads, n_kv_heads, head_dim, scale, wi
     with _span(op, *_attention_cost(ctx, q, None, None, out, n_heads, head_dim, window,
                                     n_kv_heads)):
         if (head_dim % 16 == 0 and head_dim <= 512 and hdv == head_dim and not values_in_keys
-                and not keep_first):
-            max_keys = min(abs(window), ctx.max_len) if window else ctx.max_len
+                and not (keep_first and dist_bias is not None)):
+            # (kept first keys are walked before the window's)
+            max_keys = min(abs(window) + keep_first, ctx.max_len) if window else ctx.max_len
             attention_decode_split(q, out, view.k_pool, view.v_pool, view.page_table, ctx.slots,
                                    ctx.positions, view.page, view.cap, n_heads, n_kv_heads,
                                    head_dim, scale, window, max(1, max_keys), sinks=sinks,
-                                   dist_bias=dist_bias)
+                                   dist_bias=dist_bias, keep_first=keep_first)
         else:
             attention_paged_simt(q, out, view.k_pool, view.v_pool, view.page_table, ctx.slots,
                                  ctx.positions, ctx.seq_index, view.page, view.cap, n_heads,

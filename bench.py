@@ -37,7 +37,11 @@ dense squared-relu feed-forward) beside a Gemma 3 decoder of equal width, heads,
 vocabulary whose every second layer has the same window and whose gated feed-forward has as
 many weights.  ``--compare bovozen`` sets the Bovozen decoder (attention over blocks of positions
 alternating with the gated delta rule, routed experts beside a gated shared one) beside the
-Ramilorn decoder of equal width, heads, experts, layers and vocabulary.
+Ramilorn decoder of equal width, heads, experts, layers and vocabulary.  ``--compare kadavik``
+sets the Kadavik decoder (attention with a convolution on q, k and v, a window behind which the
+first keys stay visible and an output gate, alternating with the matrix memory; routed experts
+with identity experts beside a gated shared one; a per-layer token input) beside the Bovozen
+decoder of equal width, heads, head size, experts, layers and vocabulary.
 """
 import argparse
 import json
@@ -319,7 +323,33 @@ def compare_configs_bovozen(size):
     return bovozen, compare_configs(size)[0]
 
 
+def compare_configs_kadavik(size):
+    """Kadavik beside Bovozen, the library's other decoder with a recurrent mixer, routed
+    experts and a shared one: equal width, heads, head size, experts, layers and vocabulary.
+    Kadavik's layers alternate attention (four taps on q, k and v, half the head rotated, a
+    window of 1,024 behind which four keys stay, an output gate) with the matrix memory (as
+    many heads, state head size x head size per head); its routers have two identity outputs
+    beyond the experts; every layer takes a token input 64 wide."""
+    H, A, G, d, E, top, ff, groups, keep, L, V = COMPARE_SIZES[size]
+    att = {"conv": 4, "dim": d, "heads": A, "kv_heads": G,
+           "mask": {"keep_first": 4, "size": 1024},
+           "rot": {"base": 500000.0, "dims": d // 2,
+                   "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}},
+           "scale": d ** -0.5, "vdim": d}
+    rec = {"dim": d, "gate_cap": 15.0, "heads": A, "vdim": d}
+    mlp = {"expert": {"ff": ff}, "kind": "moe",
+           "router": {"experts": E, "identity": 2, "scale": 2.0, "top": top},
+           "shared": {"ff": 2 * ff}}
+    layers = [{"mixer": rec if l % 2 else att, "mlp": mlp,
+               "type": "mlstm" if l % 2 else "attention"} for l in range(L)]
+    kadavik = {"architecture": "Kadavik", "embedding": {"scale": H ** 0.5}, "layers": layers,
+               "logit_scale": 1.0, "norm": {"eps": 1e-6}, "token_side": {"dim": 64}, "vocab": V,
+               "width": H}
+    return kadavik, compare_configs_bovozen(size)[0]
+
+
 COMPARE_BUILDERS = {"ramilorn": (compare_configs, "gemma3"),
+                    "kadavik": (compare_configs_kadavik, "bovozen"),
                     "zazerax": (compare_configs_zazerax, "gemma3"),
                     "bovozen": (compare_configs_bovozen, "ramilorn")}
 

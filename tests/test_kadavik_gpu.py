@@ -501,7 +501,8 @@ def _mark_weights(W, m, td, strength=1.6):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("size, keep, taps, d, dv", [(72, 4, 4, 64, 64), (20, 3, 2, 24, 16),
-                                                      (64, 1, 3, 32, 32), (130, 7, None, 16, 16)])
+                                                      (64, 1, 3, 32, 32), (130, 7, None, 16, 16),
+                                                      (100, 70, 2, 128, 128), (90, 5, 3, 64, 32)])
 def test_the_key_at_a_window_edge_or_a_kept_place_decides(dtype, size, keep, taps, d, dv):
     """One key scores far above the rest.  It is placed at the last kept first place, at the
     first place that is not kept, and so that it lies just inside or just outside the window
@@ -523,6 +524,52 @@ def test_the_key_at_a_window_edge_or_a_kept_place_decides(dtype, size, keep, tap
         part = _attention_part(W, m, H, td)
         for new in ([T], [mark + 3] + [1] * (T - mark - 3), [T - 9] + [1] * 9):
             assert rel_err(_run_alone(part, h, new, td), ref) < tol, (mark, new[:2])
+
+
+@pytest.mark.parametrize("hd, window, keep, T", [(64, 72, 4, 300), (128, 100, 70, 260),
+                                                 (32, 64, 1, 200), (64, 130, 65, 400)])
+def test_kept_keys_in_every_form_of_the_prompt_kernels(hd, window, keep, T):
+    """bfloat16: the one-warp, the mma.sync and the tcgen05 prompt kernels on the same q, k, v
+    (two sequences of unequal lengths, peaked scores) against sums written out in torch."""
+    from agave_b200 import kernels
+    nh, nkv = 4, 2
+    lens = [T, T // 3]
+    q = rnd(sum(lens), nh * hd, seed=5, std=1.0).to(torch.bfloat16).to(DEV)
+    k = rnd(sum(lens), nkv * hd, seed=6, std=1.0).to(torch.bfloat16).to(DEV)
+    v = rnd(sum(lens), nkv * hd, seed=7, std=1.0).to(torch.bfloat16).to(DEV)
+    scale = 2.0 / hd ** 0.5
+    i32 = dict(dtype=torch.int32, device=DEV)
+    cu = torch.tensor([0, lens[0], sum(lens)], **i32)
+    pos = torch.tensor(list(range(lens[0])) + list(range(lens[1])), **i32)
+    seq = torch.tensor([0] * lens[0] + [1] * lens[1], **i32)
+    ref = torch.zeros(sum(lens), nh, hd, dtype=torch.float64)
+    o = 0
+    for n in lens:
+        i = torch.arange(n)[:, None]
+        j = torch.arange(n)[None, :]
+        see = (j <= i) & ((i - j < window) | (j < keep))
+        for a in range(nh):
+            g = a // (nh // nkv)
+            sc = q[o:o + n, a * hd:(a + 1) * hd].double().cpu() @ \
+                k[o:o + n, g * hd:(g + 1) * hd].double().cpu().T * scale
+            sc = torch.where(see, sc, torch.full_like(sc, -math.inf))
+            ref[o:o + n, a] = torch.softmax(sc, -1) @ v[o:o + n, g * hd:(g + 1) * hd].double().cpu()
+        o += n
+    ref = ref.reshape(sum(lens), nh * hd)
+    out = torch.empty(sum(lens), nh * hd, dtype=torch.bfloat16, device=DEV)
+    kernels.attention_prefill_simt(q, k, v, out, pos, seq, cu, nh, nkv, hd, scale, window,
+                                   keep_first=keep)
+    assert rel_err(out, ref) < 2e-2
+    out.zero_()
+    kernels.attention_prefill_mma(q, k, v, out, cu, max(lens), nh, nkv, hd, scale, window,
+                                  keep_first=keep)
+    assert rel_err(out, ref) < 2e-2
+    if hd % 16 == 0:
+        out.zero_()
+        kernels.attention_prefill_tc(q, k, v, out, cu, max(lens), nh, nkv, hd, scale, window,
+                                     keep_first=keep)
+        assert kernels.attention_tc_status() == 0
+        assert rel_err(out, ref) < 2e-2
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
