@@ -8,18 +8,18 @@
 //     n_t = the same with k_t alone                                            [d]
 //     o_t = S_t^T q_t / (max(|n_t . q_t|, exp(-m_t)) + den_eps)
 // S, n and m of a sequence live in 32-bit in its slot of the cache's fixed-size state
-// ([H, d, dv] | [H, d] | [H]), zero when the slot is taken, read at the start of a step and
+// ([H, d, dv] | [H, d] | [H, column blocks]), zero when the slot is taken, read at the start of a step and
 // written at its end.  A prompt and a decoded token run the same kernels.
 //
 //  * agv_mlstm_prepare: from a token's row  q | k | v | g | i | f  of the stacked projection
 //    (32-bit, or 32-bit partial sums over ranges of K): q times q_mult, k, v and the two log
 //    gates, 32-bit.
 //  * agv_mlstm_scan: the recurrence over the step's tokens, sequence by sequence.  A column
-//    of S goes to L lanes that hold 16 rows each in registers (rows l, l + L, ...); a token
-//    is one update of those rows, two dot products with q (for S and for n), one round of
-//    L-wide shuffles.  Tokens come through shared memory, a chunk at a time.
-//  * agv_mlstm_out: every head's o over its root mean square, times a weight per channel,
-//    times sigmoid(g), rounded to the compute dtype for the output product.
+//    of S goes to L lanes that hold 16 rows each in registers; n is one more such column
+//    (its value is 1).  A token is one update of those rows, one dot product with q, one round
+//    of L-wide shuffles; it leaves S_t^T q_t, n_t . q_t and exp(-m_t).
+//  * agv_mlstm_out: the division, every head's o over its root mean square, times a weight
+//    per channel, times sigmoid(g), rounded to the compute dtype for the output product.
 #include "common.cuh"
 #include "row_in.cuh"
 
@@ -53,119 +53,245 @@ mlstm_prepare_kernel(RowIn<float> in, int n_tokens, int H, int d, int dv,
     }
 }
 
-// grid (column blocks, heads, sequences); thread = column * L + lane.
+// How the columns of a head's S are dealt out: L lanes a column (L * 16 >= d), `cols` columns a
+// CTA, ceil(dv / cols) CTAs a head.  Host and device agree through this one function.
+__host__ __device__ inline void mlstm_shape(int d, int dv, int* L, int* cols, int* blocks) {
+    int l = 1;
+    while (l * ML_ROWS < d) l *= 2;
+    int c = 256 / l;
+    if (c > dv) c = dv;
+    *L = l;
+    *cols = c;
+    *blocks = (dv + c - 1) / c;
+}
+
+__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(
+                     (unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() {
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// grid (column blocks, heads, sequences).  Thread groups of L lanes: group g < cols holds
+// column blockIdx.x * cols + g of S, group `cols` holds n (a column whose value is 1; live in
+// the first column block only).  A lane's 16 rows are four quads, quad i = rows
+// (i * L + lane) * 4 .. + 3, so that a group's lanes read consecutive 16-byte pieces of k and
+// q in shared memory and all groups the same pieces.  Tokens come 16 at a time through two
+// buffers filled by asynchronous copies while the lanes work on the other; the first warp
+// turns the chunk's gate logarithms into the factors a_t = exp(f + m_(t-1) - m_t) and
+// b_t = exp(i - m_t) with a scan over the chunk (m -> max(f + m, i) composes: (f2, i2) after
+// (f1, i1) is (f1 + f2, max(f2 + i1, i2))).  The kernel leaves the read-out's numerator
+// S_t^T q_t in `num` and n_t . q_t, exp(-m_t) in `den`; the division is the next kernel's.
+// Every column block carries a copy of the head's running maximum (state m [H, blocks]), so
+// that no CTA reads what another writes.
 template <int L>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(288)
 mlstm_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ gates,
-                  float* __restrict__ out, int H, int d, int dv, float den_eps,
+                  float* __restrict__ num, float* __restrict__ den, int H, int d, int dv,
                   float* __restrict__ state, long long state_stride,
-                  const int* __restrict__ slots, const int* __restrict__ cu_seqlens, int cols) {
+                  const int* __restrict__ slots, const int* __restrict__ cu_seqlens, int cols,
+                  int blocks) {
     pdl_wait();
     pdl_launch_next();
-    extern __shared__ float sm[];
+    extern __shared__ __align__(16) float sm[];
     constexpr int DP = L * ML_ROWS;                   // rows, padded
-    float* ks = sm;                                   // [CHUNK][DP]
-    float* qs = ks + ML_CHUNK * DP;                   // [CHUNK][DP]
-    float* vs = qs + ML_CHUNK * DP;                   // [CHUNK][cols]
-    float* gs = vs + ML_CHUNK * cols;                 // [CHUNK][2]
+    constexpr int CH = ML_CHUNK;
+    const int CW = cols;                              // values staged per token
+    const int buf_len = CH * (2 * DP + CW);
+    float* coef = sm + 2 * buf_len;                   // [2][CH][2]: a, b
     const int b = blockIdx.z, h = blockIdx.y;
     const int t0 = cu_seqlens[b], t1 = cu_seqlens[b + 1];
     const int slot = slots[b];
-    const int col = blockIdx.x * cols + threadIdx.x / L, lane = threadIdx.x % L;
-    const bool live = col < dv && threadIdx.x / L < cols;
+    const int grp = threadIdx.x / L, lane = threadIdx.x % L;
+    const bool is_n = grp == cols;
+    const int col = blockIdx.x * cols + grp;
+    const bool live = is_n ? blockIdx.x == 0 : (grp < cols && col < dv);
     const int nq = H * d, C = 2 * nq + H * dv;
     if (slot < 0) {
         // a padding entry: its rows are written, with zeros
-        for (int t = t0; t < t1; ++t)
-            if (live && lane == 0) out[(size_t)t * H * dv + (size_t)h * dv + col] = 0.f;
+        for (int t = t0; t < t1; ++t) {
+            if (live && lane == 0 && !is_n) num[(size_t)t * H * dv + (size_t)h * dv + col] = 0.f;
+            if (live && lane == 0 && is_n) {
+                den[((size_t)t * H + h) * 2] = 0.f;
+                den[((size_t)t * H + h) * 2 + 1] = 1.f;
+            }
+        }
         return;
     }
     float* st = state + (size_t)slot * state_stride;
     float* S_g = st + (size_t)h * d * dv;
     float* n_g = st + (size_t)H * d * dv + (size_t)h * d;
-    float* m_g = st + (size_t)H * d * dv + (size_t)H * d + h;
-    float S[ML_ROWS], n[ML_ROWS];
+    float* m_g = st + (size_t)H * d * dv + (size_t)H * d + (size_t)h * blocks + blockIdx.x;
+    float S[ML_ROWS];
 #pragma unroll
-    for (int i = 0; i < ML_ROWS; ++i) {
-        const int r = lane + L * i;
-        S[i] = live && r < d ? S_g[(size_t)r * dv + col] : 0.f;
-        n[i] = r < d ? n_g[r] : 0.f;
-    }
-    float m = *m_g;
-    for (int c0 = t0; c0 < t1; c0 += ML_CHUNK) {
-        const int nt = min(ML_CHUNK, t1 - c0);
-        __syncthreads();                              // everybody is past the chunk before
-        for (int idx = threadIdx.x; idx < nt * DP; idx += blockDim.x) {
-            const int tt = idx / DP, r = idx % DP;
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int r = (i * L + lane) * 4 + c;
+            S[i * 4 + c] = !live || r >= d ? 0.f : is_n ? n_g[r] : S_g[(size_t)r * dv + col];
+        }
+    // the padding rows of both buffers stay zero
+    for (int i = threadIdx.x; i < 2 * buf_len; i += blockDim.x) sm[i] = 0.f;
+    __syncthreads();
+    float m_in = *m_g;                                // (used by the first warp)
+    const int n_chunks = (t1 - t0 + CH - 1) / CH;
+    auto issue = [&](int c) {
+        float* qs = sm + (c & 1) * buf_len;
+        float* ks = qs + CH * DP;
+        float* vs = ks + CH * DP;
+        const int c0 = t0 + c * CH, nt = min(CH, t1 - c0);
+        // a warp a token, lanes along the row: no division in the walk
+        const int warp = threadIdx.x >> 5, ln = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+        for (int tt = warp; tt < nt; tt += n_warps) {
             const float* row = qkv + (size_t)(c0 + tt) * C + (size_t)h * d;
-            qs[idx] = r < d ? row[r] : 0.f;
-            ks[idx] = r < d ? row[nq + r] : 0.f;
+            for (int r = ln; r < d; r += 32) {
+                cp_async4(qs + tt * DP + r, row + r);
+                cp_async4(ks + tt * DP + r, row + nq + r);
+            }
+            const float* vrow = qkv + (size_t)(c0 + tt) * C + 2 * nq + (size_t)h * dv +
+                                (size_t)blockIdx.x * cols;
+            const int nv = min(CW, dv - (int)blockIdx.x * cols);
+            for (int g = ln; g < nv; g += 32) cp_async4(vs + tt * CW + g, vrow + g);
         }
-        for (int idx = threadIdx.x; idx < nt * cols; idx += blockDim.x) {
-            const int tt = idx / cols, c = blockIdx.x * cols + idx % cols;
-            vs[idx] = c < dv ? qkv[(size_t)(c0 + tt) * C + 2 * nq + (size_t)h * dv + c] : 0.f;
+        cp_async_commit();
+    };
+    // the first warp's lanes hold the gate logarithms of the chunk they turn into factors next
+    float gi = -INFINITY, gf = 0.f;
+    auto load_gates = [&](int c) {
+        const int c0 = t0 + c * CH, nt = min(CH, t1 - c0);
+        gi = -INFINITY, gf = 0.f;                     // (beyond the chunk: m stays)
+        if (threadIdx.x < nt) {
+            gi = gates[(size_t)(c0 + threadIdx.x) * 2 * H + h];
+            gf = gates[(size_t)(c0 + threadIdx.x) * 2 * H + H + h];
         }
-        for (int idx = threadIdx.x; idx < nt * 2; idx += blockDim.x) {
-            const int tt = idx >> 1, which = idx & 1;
-            gs[idx] = gates[(size_t)(c0 + tt) * 2 * H + which * H + h];
+    };
+    if (n_chunks > 0) {
+        issue(0);
+        if (threadIdx.x < 32) load_gates(0);
+    }
+    for (int c = 0; c < n_chunks; ++c) {
+        const int c0 = t0 + c * CH, nt = min(CH, t1 - c0);
+        float* cf = coef + (c & 1) * CH * 2;
+        if (threadIdx.x < 32) {
+            // scan of the chunk's gates: lane t ends with the map of tokens 0..t composed.  The
+            // sums are 64-bit and every m_t is rounded to 32 bits once, so that the exponents
+            // f + m_(t-1) - m_t carry the roundings of the m's they are formed from (a forget
+            // gate next to one moves m by less than its last bit a token)
+            double F = gf, I = gi;
+#pragma unroll
+            for (int o = 1; o < CH; o <<= 1) {
+                const double Fp = __shfl_up_sync(0xffffffffu, F, o);
+                const double Ip = __shfl_up_sync(0xffffffffu, I, o);
+                if ((int)threadIdx.x >= o) {
+                    I = fmax(F + Ip, I);
+                    F += Fp;
+                }
+            }
+            const float m_t = (float)fmax(F + (double)m_in, I);
+            float m_p = __shfl_up_sync(0xffffffffu, m_t, 1);
+            if (threadIdx.x == 0) m_p = m_in;
+            if (threadIdx.x < nt) {
+                cf[threadIdx.x * 2] = expf((float)((double)gf + (double)m_p - (double)m_t));
+                cf[threadIdx.x * 2 + 1] = expf((float)((double)gi - (double)m_t));
+                if (blockIdx.x == 0) den[((size_t)(c0 + threadIdx.x) * H + h) * 2 + 1] = expf(-m_t);
+            }
+            m_in = __shfl_sync(0xffffffffu, m_t, nt - 1);
+        }
+        if (c + 1 < n_chunks) {
+            issue(c + 1);
+            if (threadIdx.x < 32) load_gates(c + 1);
+            cp_async_wait<1>();                       // chunk c has landed, c + 1 is under way
+        } else {
+            cp_async_wait<0>();
         }
         __syncthreads();
-        for (int tt = 0; tt < nt; ++tt) {
-            const float gi = gs[2 * tt], gf = gs[2 * tt + 1];
-            const float m_new = fmaxf(gf + m, gi);
-            const float a = expf(gf + m - m_new), w = expf(gi - m_new);
-            m = m_new;
-            const float wv = w * vs[tt * cols + threadIdx.x / L];
-            const float* kr = ks + tt * DP + lane;
-            const float* qr = qs + tt * DP + lane;
-            float ds = 0.f, dn = 0.f;
+        const float* qs = sm + (c & 1) * buf_len;
+        const float* ks = qs + CH * DP;
+        const float* vs = ks + CH * DP;
+        // a token's sum over its lanes and its store run under the next token's loads
+        float pend = 0.f;
+        auto finish = [&](int tt, float ds) {
 #pragma unroll
-            for (int i = 0; i < ML_ROWS; ++i) {
-                const float kk = kr[L * i], qq = qr[L * i];
-                S[i] = fmaf(a, S[i], wv * kk);
-                n[i] = fmaf(a, n[i], w * kk);
-                ds = fmaf(S[i], qq, ds);
-                dn = fmaf(n[i], qq, dn);
-            }
-#pragma unroll
-            for (int o = L >> 1; o > 0; o >>= 1) {
-                ds += __shfl_xor_sync(0xffffffffu, ds, o);
-                dn += __shfl_xor_sync(0xffffffffu, dn, o);
-            }
+            for (int o = L >> 1; o > 0; o >>= 1) ds += __shfl_xor_sync(0xffffffffu, ds, o);
             if (live && lane == 0) {
-                const float den = fmaxf(fabsf(dn), expf(-m)) + den_eps;
-                out[(size_t)(c0 + tt) * H * dv + (size_t)h * dv + col] = ds / den;
+                if (is_n) den[((size_t)(c0 + tt) * H + h) * 2] = ds;
+                else num[(size_t)(c0 + tt) * H * dv + (size_t)h * dv + col] = ds;
             }
-        }
-    }
-    if (t1 > t0) {
+        };
+        const int vcol = min(grp, CW - 1);
+#pragma unroll 2
+        for (int tt = 0; tt < nt; ++tt) {
+            const float a = cf[tt * 2], w = cf[tt * 2 + 1];
+            const float vj = vs[tt * CW + vcol];
+            const float4* k4 = reinterpret_cast<const float4*>(ks + tt * DP) + lane;
+            const float4* q4 = reinterpret_cast<const float4*>(qs + tt * DP) + lane;
+            float4 kk[4], qq[4];
 #pragma unroll
-        for (int i = 0; i < ML_ROWS; ++i) {
-            const int r = lane + L * i;
-            if (live && r < d) S_g[(size_t)r * dv + col] = S[i];
-            if (blockIdx.x == 0 && threadIdx.x < L && r < d) n_g[r] = n[i];
+            for (int i = 0; i < 4; ++i) {
+                kk[i] = k4[i * L];
+                qq[i] = q4[i * L];
+            }
+            if (tt > 0) finish(tt - 1, pend);
+            const float wv = is_n ? w : w * vj;
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                S[i * 4 + 0] = fmaf(wv, kk[i].x, a * S[i * 4 + 0]);
+                S[i * 4 + 1] = fmaf(wv, kk[i].y, a * S[i * 4 + 1]);
+                S[i * 4 + 2] = fmaf(wv, kk[i].z, a * S[i * 4 + 2]);
+                S[i * 4 + 3] = fmaf(wv, kk[i].w, a * S[i * 4 + 3]);
+                acc[0] = fmaf(S[i * 4 + 0], qq[i].x, acc[0]);
+                acc[1] = fmaf(S[i * 4 + 1], qq[i].y, acc[1]);
+                acc[2] = fmaf(S[i * 4 + 2], qq[i].z, acc[2]);
+                acc[3] = fmaf(S[i * 4 + 3], qq[i].w, acc[3]);
+            }
+            pend = (acc[0] + acc[1]) + (acc[2] + acc[3]);
         }
-        if (blockIdx.x == 0 && threadIdx.x == 0) *m_g = m;
+        if (nt > 0) finish(nt - 1, pend);
+        __syncthreads();                              // everybody is done with this buffer
     }
+    if (t1 > t0 && live) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int r = (i * L + lane) * 4 + c;
+                if (r < d) {
+                    if (is_n) n_g[r] = S[i * 4 + c];
+                    else S_g[(size_t)r * dv + col] = S[i * 4 + c];
+                }
+            }
+    }
+    if (t1 > t0 && threadIdx.x == 0) *m_g = m_in;
 }
 
-// One warp per (token, head).
+// One warp per (token, head): the read-out o = num / (max(|n . q|, exp(-m)) + den_eps), over
+// its root mean square, times the weight, times sigmoid(g).
 template <typename T>
 __global__ void __launch_bounds__(128)
-mlstm_out_kernel(const float* __restrict__ o, RowIn<float> in, int gate_off,
-                 const float* __restrict__ weight, float eps, int n_tokens, int H, int dv,
-                 T* __restrict__ y) {
+mlstm_out_kernel(const float* __restrict__ num, const float* __restrict__ den, float den_eps,
+                 RowIn<float> in, int gate_off, const float* __restrict__ weight, float eps,
+                 int n_tokens, int H, int dv, T* __restrict__ y) {
     pdl_wait();
     pdl_launch_next();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long item = (long long)blockIdx.x * 4 + warp;
     if (item >= (long long)n_tokens * H) return;
     const int t = (int)(item / H), h = (int)(item % H);
-    const float* row = o + ((size_t)t * H + h) * dv;
+    const float* row = num + ((size_t)t * H + h) * dv;
+    const float2 dn = *reinterpret_cast<const float2*>(den + ((size_t)t * H + h) * 2);
+    const float inv_den = 1.0f / (fmaxf(fabsf(dn.x), dn.y) + den_eps);
     float ss = 0.f;
-    for (int e = lane; e < dv; e += 32) ss = fmaf(row[e], row[e], ss);
+    for (int e = lane; e < dv; e += 32) {
+        const float o = row[e] * inv_den;
+        ss = fmaf(o, o, ss);
+    }
     ss = warp_sum(ss);
-    const float inv = rsqrtf(ss / (float)dv + eps);
+    const float inv = rsqrtf(ss / (float)dv + eps) * inv_den;
     for (int e = lane; e < dv; e += 32) {
         const float g = in.at(t, gate_off + h * dv + e);
         y[((size_t)t * H + h) * dv + e] =
@@ -198,27 +324,39 @@ AGV_API int agv_mlstm_prepare(const float* row, long long ld, const float* part,
     return 0;
 }
 
-AGV_API int agv_mlstm_state_numel(int H, int d, int dv) { return H * d * dv + H * d + H; }
+AGV_API int agv_mlstm_state_numel(int H, int d, int dv) {
+    int L, cols, blocks;
+    mlstm_shape(d, dv, &L, &cols, &blocks);
+    return H * d * dv + H * d + H * blocks;
+}
 
-AGV_API int agv_mlstm_scan(const float* qkv, const float* gates, float* out, int T, int B, int H,
-                           int d, int dv, float den_eps, float* state, long long state_stride,
+// qkv [T, 2 H d + H dv] and gates [T, 2 H] from agv_mlstm_prepare; num [T, H dv] receives
+// S_t^T q_t and den [T, H, 2] receives n_t . q_t and exp(-m_t); state [n_slots, stride] holds
+// S [H, d, dv], n [H, d] and a copy of m per column block [H, blocks] of every sequence.
+AGV_API int agv_mlstm_scan(const float* qkv, const float* gates, float* num, float* den, int T,
+                           int B, int H, int d, int dv, float* state, long long state_stride,
                            const int* slots, const int* cu_seqlens, cudaStream_t stream) {
     AGV_REQUIRE(T >= 0 && B > 0 && H > 0 && d > 0 && dv > 0, "mlstm_scan: bad sizes");
     AGV_REQUIRE(d <= 16 * ML_ROWS, "mlstm_scan: head size %d exceeds %d", d, 16 * ML_ROWS);
     AGV_REQUIRE(state_stride >= agv_mlstm_state_numel(H, d, dv), "mlstm_scan: state too small");
+    AGV_REQUIRE(agv_aligned(den, 8), "mlstm_scan: den must be 8-byte aligned");
     if (T == 0) return 0;
-    int L = 1;
-    while (L * ML_ROWS < d) L *= 2;
-    int cols = 256 / L;
-    if (cols > dv) cols = dv;
-    // (a warp holds whole columns: cols * L is rounded up to a warp by idle threads)
-    const int threads = (cols * L + 31) / 32 * 32;
-    const dim3 grid((unsigned)((dv + cols - 1) / cols), (unsigned)H, (unsigned)B);
-    const size_t smem = ((size_t)2 * ML_CHUNK * L * ML_ROWS + (size_t)ML_CHUNK * cols +
-                         2 * ML_CHUNK) * sizeof(float);
-#define AGV_SCAN(LL)                                                                           \
-    agv_launch_after(mlstm_scan_kernel<LL>, grid, threads, smem, stream, qkv, gates, out, H, d, \
-                     dv, den_eps, state, state_stride, slots, cu_seqlens, cols)
+    int L, cols, blocks;
+    mlstm_shape(d, dv, &L, &cols, &blocks);
+    // (a warp holds whole groups: (cols + 1) * L is rounded up to a warp by idle threads)
+    const int threads = ((cols + 1) * L + 31) / 32 * 32;
+    const dim3 grid((unsigned)blocks, (unsigned)H, (unsigned)B);
+    const size_t smem = ((size_t)2 * ML_CHUNK * (2 * L * ML_ROWS + cols) + 4 * ML_CHUNK) *
+                        sizeof(float);
+#define AGV_SCAN(LL)                                                                          \
+    do {                                                                                      \
+        auto kern = mlstm_scan_kernel<LL>;                                                    \
+        if (smem > 48 * 1024)                                                                 \
+            AGV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                             (int)smem));                                     \
+        agv_launch_after(kern, grid, threads, smem, stream, qkv, gates, num, den, H, d, dv,   \
+                         state, state_stride, slots, cu_seqlens, cols, blocks);               \
+    } while (0)
     switch (L) {
         case 1: AGV_SCAN(1); break;
         case 2: AGV_SCAN(2); break;
@@ -231,9 +369,10 @@ AGV_API int agv_mlstm_scan(const float* qkv, const float* gates, float* out, int
     return 0;
 }
 
-AGV_API int agv_mlstm_out(const float* o, const float* row, long long ld, const float* part,
-                          int n_splits, const float* weight, float eps, int T, int H, int d,
-                          int dv, void* y, int dtype, cudaStream_t stream) {
+AGV_API int agv_mlstm_out(const float* num, const float* den, float den_eps, const float* row,
+                          long long ld, const float* part, int n_splits, const float* weight,
+                          float eps, int T, int H, int d, int dv, void* y, int dtype,
+                          cudaStream_t stream) {
     AGV_REQUIRE(T >= 0 && H > 0 && dv > 0, "mlstm_out: bad sizes");
     if (T == 0) return 0;
     RowIn<float> in;
@@ -241,11 +380,11 @@ AGV_API int agv_mlstm_out(const float* o, const float* row, long long ld, const 
     const int gate_off = 2 * H * d + H * dv;
     const unsigned grid = (unsigned)(((long long)T * H + 3) / 4);
     if (dtype == AGV_F32)
-        agv_launch(mlstm_out_kernel<float>, grid, 128, 0, stream, o, in, gate_off, weight, eps, T,
-                   H, dv, (float*)y);
+        agv_launch(mlstm_out_kernel<float>, grid, 128, 0, stream, num, den, den_eps, in, gate_off,
+                   weight, eps, T, H, dv, (float*)y);
     else if (dtype == AGV_BF16)
-        agv_launch(mlstm_out_kernel<__nv_bfloat16>, grid, 128, 0, stream, o, in, gate_off, weight,
-                   eps, T, H, dv, (__nv_bfloat16*)y);
+        agv_launch(mlstm_out_kernel<__nv_bfloat16>, grid, 128, 0, stream, num, den, den_eps, in,
+                   gate_off, weight, eps, T, H, dv, (__nv_bfloat16*)y);
     else
         return agv_fail(-1, "mlstm_out: unknown dtype %d", dtype);
     AGV_LAUNCH_OK("mlstm_out_kernel");

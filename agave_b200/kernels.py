@@ -897,9 +897,22 @@ def delta_out(o: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, eps: float, 
 
 
 # ------------------------------------------------------- matrix memory (mLSTM)
+def mlstm_shape(head_dim: int, value_dim: int):
+    """(lanes a column, columns a CTA, CTAs a head) of the matrix memory's scan: a column of S
+    goes to L lanes of 16 rows each, L a power of two with L * 16 >= head_dim; a CTA takes up
+    to 256 / L columns.  (The same rule stands in ``csrc/mlstm.cu``.)"""
+    lanes = 1
+    while lanes * 16 < head_dim:
+        lanes *= 2
+    cols = min(256 // lanes, value_dim)
+    return lanes, cols, (value_dim + cols - 1) // cols
+
+
 def mlstm_state_numel(n_heads: int, head_dim: int, value_dim: int) -> int:
-    """32-bit values a sequence's matrix memory takes: S [H, d, dv], n [H, d], m [H]."""
-    return n_heads * head_dim * value_dim + n_heads * head_dim + n_heads
+    """32-bit values a sequence's matrix memory takes: S [H, d, dv], n [H, d] and the running
+    maximum m, of which every CTA of a head keeps a copy [H, CTAs a head]."""
+    return (n_heads * head_dim * value_dim + n_heads * head_dim +
+            n_heads * mlstm_shape(head_dim, value_dim)[2])
 
 
 def _f32_row_input(row, partial, T, W):
@@ -935,40 +948,46 @@ def mlstm_prepare(row: Optional[torch.Tensor], partial: Optional[torch.Tensor], 
                                            _stream()))
 
 
-def mlstm_scan(qkv: torch.Tensor, gates: torch.Tensor, out: torch.Tensor, ctx,
-               state: torch.Tensor, n_heads: int, head_dim: int, value_dim: int,
-               den_eps: float) -> None:
+def mlstm_scan(qkv: torch.Tensor, gates: torch.Tensor, num: torch.Tensor, den: torch.Tensor, ctx,
+               state: torch.Tensor, n_heads: int, head_dim: int, value_dim: int) -> None:
     """The recurrence  m' = max(f + m, i); S <- exp(f + m - m') S + exp(i - m') k v^T; n likewise
-    with k; o = S^T q / (max(|n . q|, exp(-m')) + den_eps)  over the step's tokens, sequence by
-    sequence; S, n and m of each sequence are read from and written to ``state``.  All 32-bit;
-    out [T, H * dv]."""
+    with k  over the step's tokens, sequence by sequence; S, n and m of each sequence are read
+    from and written to ``state``.  num [T, H * dv] receives S^T q, den [T, H, 2] receives n . q
+    and exp(-m'): the read-out is num / (max(|n . q|, exp(-m')) + eps).  All 32-bit."""
     T = qkv.shape[0]
     H, d, dv = n_heads, head_dim, value_dim
-    for t, n in ((qkv, "qkv"), (gates, "gates"), (out, "out")):
+    for t, n in ((qkv, "qkv"), (gates, "gates"), (num, "num"), (den, "den")):
         _f32(t, n); _dense(t, n)
     assert qkv.shape == (T, 2 * H * d + H * dv) and gates.shape == (T, 2 * H)
-    assert out.shape == (T, H * dv)
+    assert num.shape == (T, H * dv) and den.shape == (T, H, 2)
     sp, ss = _state_args(state)
-    with _span("mlstm_scan", _nbytes(qkv, gates, out), 6 * T * H * d * dv):
-        _check(library().agv_mlstm_scan(_ptr(qkv), _ptr(gates), _ptr(out), T, ctx.batch, H, d, dv,
-                                        ctypes.c_float(den_eps), sp, ss, _ptr(ctx.slots),
-                                        _ptr(ctx.cu_seqlens), _stream()))
+    lib = library()
+    assert lib.agv_mlstm_state_numel(H, d, dv) == mlstm_state_numel(H, d, dv)
+    with _span("mlstm_scan", _nbytes(qkv, gates, num, den), 6 * T * H * d * dv):
+        _check(lib.agv_mlstm_scan(_ptr(qkv), _ptr(gates), _ptr(num), _ptr(den), T, ctx.batch, H,
+                                  d, dv, sp, ss, _ptr(ctx.slots), _ptr(ctx.cu_seqlens),
+                                  _stream()))
 
 
-def mlstm_out(o: torch.Tensor, row: Optional[torch.Tensor], partial: Optional[torch.Tensor],
-              weight: torch.Tensor, eps: float, n_heads: int, head_dim: int, value_dim: int,
-              y: torch.Tensor) -> None:
-    """y[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * weight[h, :] * sigmoid(g[t, h, :]), g the
-    gate's logits in the stacked projection (``row`` / ``partial`` as in ``mlstm_prepare``);
-    o 32-bit [T, H * dv], y in the compute dtype."""
-    T = o.shape[0]
+def mlstm_out(num: torch.Tensor, den: torch.Tensor, den_eps: float, row: Optional[torch.Tensor],
+              partial: Optional[torch.Tensor], weight: torch.Tensor, eps: float, n_heads: int,
+              head_dim: int, value_dim: int, y: torch.Tensor) -> None:
+    """o = num / (max(|den[..., 0]|, den[..., 1]) + den_eps);  y[t, h, :] = o[t, h, :] /
+    rms(o[t, h, :]) * weight[h, :] * sigmoid(g[t, h, :]), g the gate's logits in the stacked
+    projection (``row`` / ``partial`` as in ``mlstm_prepare``); num and den 32-bit, y in the
+    compute dtype."""
+    T = num.shape[0]
     H, d, dv = n_heads, head_dim, value_dim
     rp, ld, pp, ns = _f32_row_input(row, partial, T, 2 * H * d + 2 * H * dv + 2 * H)
-    _f32(o, "o"); _f32(weight, "weight"); _dense(o, "o"); _dense(weight, "weight"); _dense(y, "y")
-    assert o.shape == y.shape == (T, H * dv) and weight.numel() == H * dv
-    with _span("mlstm_out", _nbytes(o, y) + T * H * dv * 4):
-        _check(library().agv_mlstm_out(_ptr(o), rp, ld, pp, ns, _ptr(weight), ctypes.c_float(eps),
-                                       T, H, d, dv, _ptr(y), dtype_code(y.dtype), _stream()))
+    for t, n in ((num, "num"), (den, "den"), (weight, "weight")):
+        _f32(t, n); _dense(t, n)
+    _dense(y, "y")
+    assert num.shape == y.shape == (T, H * dv) and den.shape == (T, H, 2)
+    assert weight.numel() == H * dv
+    with _span("mlstm_out", _nbytes(num, den, y) + T * H * dv * 4):
+        _check(library().agv_mlstm_out(_ptr(num), _ptr(den), ctypes.c_float(den_eps), rp, ld, pp,
+                                       ns, _ptr(weight), ctypes.c_float(eps), T, H, d, dv,
+                                       _ptr(y), dtype_code(y.dtype), _stream()))
 
 
 # ------------------------------------------- attention with a short convolution

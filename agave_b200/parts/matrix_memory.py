@@ -13,11 +13,11 @@ sigmoid(W_g x), and goes through the output product.
 
 Flow of a step: one stacked product  q | k | v | g | i | f  into 32-bit sums; a row kernel
 (q scaled, the two gates capped and taken to logarithms); the scan over the step's tokens,
-sequence by sequence; the read-out row kernel (norm, weight, gate, rounding); the output
-product.  A prompt and a decoded token run the same kernels: S [H, d, dv], n [H, d] and m [H]
-live in 32-bit in the sequence's slot of the cache's fixed-size state (``StateRequest``), zero
-when the slot is taken (the running maximum's start), read at the start of a step and written
-at its end.
+sequence by sequence, which leaves S^T q, n . q and exp(-m); the read-out row kernel (the
+division, norm, weight, gate, rounding); the output product.  A prompt and a decoded token run
+the same kernels: S [H, d, dv], n [H, d] and m (a copy per CTA of a head's scan) live in 32-bit
+in the sequence's slot of the cache's fixed-size state (``StateRequest``), zero when the slot
+is taken (the running maximum's start), read at the start of a step and written at its end.
 """
 from __future__ import annotations
 
@@ -102,10 +102,12 @@ class MatrixMemoryMixer:
         gates = ctx.new(T, 2 * H, dtype=f32)
         kernels.mlstm_prepare(row, part, T, H, d, dv, self.bias_i, self.bias_f, float(s.gate_cap),
                               float(d) ** -0.5, qkv, gates)
-        o = ctx.new(T, H * dv, dtype=f32)
-        kernels.mlstm_scan(qkv, gates, o, ctx, state, H, d, dv, float(s.den_eps))
+        num = ctx.new(T, H * dv, dtype=f32)
+        den = ctx.new(T, H, 2, dtype=f32)
+        kernels.mlstm_scan(qkv, gates, num, den, ctx, state, H, d, dv)
         y = ctx.new(T, H * dv)
-        kernels.mlstm_out(o, row, part, self.out_norm, float(s.eps), H, d, dv, y)
+        kernels.mlstm_out(num, den, float(s.den_eps), row, part, self.out_norm, float(s.eps), H, d,
+                          dv, y)
         return self.out.partial(y)
 
 

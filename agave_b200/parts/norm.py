@@ -49,6 +49,10 @@ class RMSNorm:
                 nxt.forward(h, x_out)
         elif nxt is None or isinstance(nxt, RMSNorm):
             fused_residual(h, y, self, nxt, x_out)
+        elif isinstance(nxt, Identity):
+            # the stream itself, rounded, is what follows: one launch
+            kernels.layer_norm_join(h, y, self.weight, None, None, None, x_out,
+                                    eps_post=self.eps, rms=True)
         else:
             fused_residual(h, y, self, None, None)
             nxt.forward(h, x_out)
