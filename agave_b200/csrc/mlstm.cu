@@ -8,7 +8,7 @@
 //     n_t = the same with k_t alone                                            [d]
 //     o_t = S_t^T q_t / (max(|n_t . q_t|, exp(-m_t)) + den_eps)
 // S, n and m of a sequence live in 32-bit in its slot of the cache's fixed-size state
-// ([H, d, dv] | [H, d] | [H, column blocks]), zero when the slot is taken, read at the start of a step and
+// ([H, d, dv] | [H, d] | [H, ceil(dv / 8)]), zero when the slot is taken, read at the start of a step and
 // written at its end.  A prompt and a decoded token run the same kernels.
 //
 //  * agv_mlstm_prepare: from a token's row  q | k | v | g | i | f  of the stacked projection
@@ -53,17 +53,17 @@ mlstm_prepare_kernel(RowIn<float> in, int n_tokens, int H, int d, int dv,
     }
 }
 
-// How the columns of a head's S are dealt out: L lanes a column (L * 16 >= d), `cols` columns a
-// CTA, ceil(dv / cols) CTAs a head.  Host and device agree through this one function.
-__host__ __device__ inline void mlstm_shape(int d, int dv, int* L, int* cols, int* blocks) {
+// How the columns of a head's S are dealt out: L lanes a column (L * 16 >= d), at most
+// 256 / L columns a CTA.  The running maximum has a copy per ML_MCOLS columns in the state, so
+// that the number of columns a CTA takes (a multiple of ML_MCOLS, or all of them) can follow
+// the size of the launch.
+constexpr int ML_MCOLS = 8;
+__host__ __device__ inline int mlstm_lanes(int d) {
     int l = 1;
     while (l * ML_ROWS < d) l *= 2;
-    int c = 256 / l;
-    if (c > dv) c = dv;
-    *L = l;
-    *cols = c;
-    *blocks = (dv + c - 1) / c;
+    return l;
 }
+__host__ __device__ inline int mlstm_m_copies(int dv) { return (dv + ML_MCOLS - 1) / ML_MCOLS; }
 
 __device__ __forceinline__ void cp_async4(float* dst, const float* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(
@@ -86,15 +86,15 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
 // b_t = exp(i - m_t) with a scan over the chunk (m -> max(f + m, i) composes: (f2, i2) after
 // (f1, i1) is (f1 + f2, max(f2 + i1, i2))).  The kernel leaves the read-out's numerator
 // S_t^T q_t in `num` and n_t . q_t, exp(-m_t) in `den`; the division is the next kernel's.
-// Every column block carries a copy of the head's running maximum (state m [H, blocks]), so
-// that no CTA reads what another writes.
+// Every group of eight columns has a copy of the head's running maximum in the state; a CTA
+// reads its first group's and writes all of its groups', so that no CTA reads what another
+// writes.
 template <int L>
 __global__ void __launch_bounds__(288)
 mlstm_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ gates,
                   float* __restrict__ num, float* __restrict__ den, int H, int d, int dv,
                   float* __restrict__ state, long long state_stride,
-                  const int* __restrict__ slots, const int* __restrict__ cu_seqlens, int cols,
-                  int blocks) {
+                  const int* __restrict__ slots, const int* __restrict__ cu_seqlens, int cols) {
     pdl_wait();
     pdl_launch_next();
     extern __shared__ __align__(16) float sm[];
@@ -125,7 +125,9 @@ mlstm_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ gates
     float* st = state + (size_t)slot * state_stride;
     float* S_g = st + (size_t)h * d * dv;
     float* n_g = st + (size_t)H * d * dv + (size_t)h * d;
-    float* m_g = st + (size_t)H * d * dv + (size_t)H * d + (size_t)h * blocks + blockIdx.x;
+    const int m_copies = mlstm_m_copies(dv);
+    float* m_g = st + (size_t)H * d * dv + (size_t)H * d + (size_t)h * m_copies +
+                 (blockIdx.x * cols) / ML_MCOLS;
     float S[ML_ROWS];
 #pragma unroll
     for (int i = 0; i < 4; ++i)
@@ -266,7 +268,10 @@ mlstm_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ gates
                 }
             }
     }
-    if (t1 > t0 && threadIdx.x == 0) *m_g = m_in;
+    if (t1 > t0 && threadIdx.x == 0) {
+        const int mine = min(cols, dv - (int)blockIdx.x * cols);
+        for (int i = 0; i * ML_MCOLS < mine; ++i) m_g[i] = m_in;
+    }
 }
 
 // One warp per (token, head): the read-out o = num / (max(|n . q|, exp(-m)) + den_eps), over
@@ -325,14 +330,12 @@ AGV_API int agv_mlstm_prepare(const float* row, long long ld, const float* part,
 }
 
 AGV_API int agv_mlstm_state_numel(int H, int d, int dv) {
-    int L, cols, blocks;
-    mlstm_shape(d, dv, &L, &cols, &blocks);
-    return H * d * dv + H * d + H * blocks;
+    return H * d * dv + H * d + H * mlstm_m_copies(dv);
 }
 
 // qkv [T, 2 H d + H dv] and gates [T, 2 H] from agv_mlstm_prepare; num [T, H dv] receives
 // S_t^T q_t and den [T, H, 2] receives n_t . q_t and exp(-m_t); state [n_slots, stride] holds
-// S [H, d, dv], n [H, d] and a copy of m per column block [H, blocks] of every sequence.
+// S [H, d, dv], n [H, d] and a copy of m per eight columns [H, ceil(dv / 8)] of every sequence.
 AGV_API int agv_mlstm_scan(const float* qkv, const float* gates, float* num, float* den, int T,
                            int B, int H, int d, int dv, float* state, long long state_stride,
                            const int* slots, const int* cu_seqlens, cudaStream_t stream) {
@@ -341,8 +344,22 @@ AGV_API int agv_mlstm_scan(const float* qkv, const float* gates, float* num, flo
     AGV_REQUIRE(state_stride >= agv_mlstm_state_numel(H, d, dv), "mlstm_scan: state too small");
     AGV_REQUIRE(agv_aligned(den, 8), "mlstm_scan: den must be 8-byte aligned");
     if (T == 0) return 0;
-    int L, cols, blocks;
-    mlstm_shape(d, dv, &L, &cols, &blocks);
+    const int L = mlstm_lanes(d);
+    // columns a CTA: as many as 256 threads hold, fewer (down to eight) while that still
+    // leaves every CTA an SM of its own.  (Measured on one prompt of 2,048 tokens, 32 heads of
+    // 128 x 128: 128 CTAs of 32 columns 851 us; 256 of 16, two to an SM, 941; 512 of 8, 1,027:
+    // a token costs a warp about 800 cycles whatever its company.)
+    int cols = 256 / L;
+    if (cols > dv) cols = dv;
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        AGV_CUDA_OK(cudaGetDevice(&dev));
+        AGV_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    }
+    while (cols % (2 * ML_MCOLS) == 0 && (long long)H * B * ((dv + cols - 1) / cols) * 2 <= sms)
+        cols /= 2;
+    const int blocks = (dv + cols - 1) / cols;
     // (a warp holds whole groups: (cols + 1) * L is rounded up to a warp by idle threads)
     const int threads = ((cols + 1) * L + 31) / 32 * 32;
     const dim3 grid((unsigned)blocks, (unsigned)H, (unsigned)B);
@@ -355,7 +372,7 @@ AGV_API int agv_mlstm_scan(const float* qkv, const float* gates, float* num, flo
             AGV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                              (int)smem));                                     \
         agv_launch_after(kern, grid, threads, smem, stream, qkv, gates, num, den, H, d, dv,   \
-                         state, state_stride, slots, cu_seqlens, cols, blocks);               \
+                         state, state_stride, slots, cu_seqlens, cols);                       \
     } while (0)
     switch (L) {
         case 1: AGV_SCAN(1); break;

@@ -897,22 +897,12 @@ def delta_out(o: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, eps: float, 
 
 
 # ------------------------------------------------------- matrix memory (mLSTM)
-def mlstm_shape(head_dim: int, value_dim: int):
-    """(lanes a column, columns a CTA, CTAs a head) of the matrix memory's scan: a column of S
-    goes to L lanes of 16 rows each, L a power of two with L * 16 >= head_dim; a CTA takes up
-    to 256 / L columns.  (The same rule stands in ``csrc/mlstm.cu``.)"""
-    lanes = 1
-    while lanes * 16 < head_dim:
-        lanes *= 2
-    cols = min(256 // lanes, value_dim)
-    return lanes, cols, (value_dim + cols - 1) // cols
-
-
 def mlstm_state_numel(n_heads: int, head_dim: int, value_dim: int) -> int:
     """32-bit values a sequence's matrix memory takes: S [H, d, dv], n [H, d] and the running
-    maximum m, of which every CTA of a head keeps a copy [H, CTAs a head]."""
+    maximum m, of which every eight columns of a head keep a copy [H, ceil(dv / 8)] (the CTAs
+    of the scan take multiples of eight columns and none reads what another writes)."""
     return (n_heads * head_dim * value_dim + n_heads * head_dim +
-            n_heads * mlstm_shape(head_dim, value_dim)[2])
+            n_heads * ((value_dim + 7) // 8))
 
 
 def _f32_row_input(row, partial, T, W):

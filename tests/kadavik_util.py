@@ -114,7 +114,19 @@ K3 = config(96, 150, [
     (attention(2, 1, 32, 32, 0.25, conv=5), moe(6, 3, 1, 16, scale=2.0)),
 ], eps=3e-6)
 
-CONFIGS = {"K1": K1, "K2": K2, "K3": K3}
+# K4: a width, a vocabulary and inner sizes that are no multiples of 8 (no product takes the
+# tensor cores), attention layers only at the end, a source with two readers.
+K4 = config(76, 211, [
+    (mlstm(2, 18, 22, 6.0), moe(3, 1, 2, 20, scale=1.2, shared=12)),
+    (mlstm(1, 40, 10, 12.0), dense(36)),
+    (attention(2, 1, 20, 12, 0.3, conv=2, size=33, keep_first=1, rot=rotation(10, 2000.0)),
+     moe(2, 2, 3, 28, scale=1.0)),
+    (attention(2, 1, 20, 12, 0.3, conv=4, size=9, keep_first=5, rot=rotation(10, 2000.0),
+               kv_from=2), None),
+    (attention(2, 1, 20, 12, 0.35, size=200, rot=rotation(10, 2000.0), kv_from=2), dense(44)),
+], eps=2e-5, embed_scale=5.0, logit_scale=1.7, side=3)
+
+CONFIGS = {"K1": K1, "K2": K2, "K3": K3, "K4": K4}
 
 
 def make_tensors(cfg, seed, dtype):

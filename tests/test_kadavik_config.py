@@ -136,7 +136,7 @@ def test_what_the_cache_is_asked_for():
     blocks = [Block(b, 72, torch.float32, dev) for b in spec.blocks]
     kv, st = blocks[0].cache_request()
     assert kv == KVRequest(2, 10, None, 14) and st == StateRequest(1 * (40 + 20 + 28))
-    assert blocks[1].cache_request() == StateRequest(3 * 12 * 10 + 3 * 12 + 3)
+    assert blocks[1].cache_request() == StateRequest(3 * 12 * 10 + 3 * 12 + 3 * 2)
     assert blocks[2].cache_request() is None and blocks[2].state_request() == StateRequest(2 * 40)
     spec3 = KadavikConfig.from_dict(CONFIGS["K3"]).to_model_spec()
     b = [Block(x, 96, torch.float32, dev) for x in spec3.blocks]
