@@ -14,10 +14,11 @@
 //  * agv_mlstm_prepare: from a token's row  q | k | v | g | i | f  of the stacked projection
 //    (32-bit, or 32-bit partial sums over ranges of K): q times q_mult, k, v and the two log
 //    gates, 32-bit.
-//  * agv_mlstm_scan: the recurrence over the step's tokens, sequence by sequence.  A column
-//    of S goes to L lanes that hold 16 rows each in registers; n is one more such column
-//    (its value is 1).  A token is one update of those rows, one dot product with q, one round
-//    of L-wide shuffles; it leaves S_t^T q_t, n_t . q_t and exp(-m_t).
+//  * agv_mlstm_scan: the recurrence over the step's tokens, sequence by sequence.  A thread
+//    holds 16 rows of one column of S in registers, a warp 32 columns, so that k and q of a
+//    token are read by a whole warp at once; the row blocks' parts of a column's dot product
+//    with q meet in shared memory after a chunk of tokens.  It leaves S_t^T q_t, n_t . q_t
+//    and exp(-m_t).
 //  * agv_mlstm_out: the division, every head's o over its root mean square, times a weight
 //    per channel, times sigmoid(g), rounded to the compute dtype for the output product.
 #include "common.cuh"
@@ -25,7 +26,8 @@
 
 namespace {
 
-constexpr int ML_ROWS = 16;          // rows of S a lane holds
+constexpr int ML_COLS = 32;          // columns of S a CTA holds, one a lane
+constexpr int ML_ROWS = 16;          // rows of a column a thread holds
 constexpr int ML_CHUNK = 16;         // tokens staged in shared memory at a time
 
 __global__ void __launch_bounds__(256)
@@ -53,16 +55,8 @@ mlstm_prepare_kernel(RowIn<float> in, int n_tokens, int H, int d, int dv,
     }
 }
 
-// How the columns of a head's S are dealt out: L lanes a column (L * 16 >= d), at most
-// 256 / L columns a CTA.  The running maximum has a copy per ML_MCOLS columns in the state, so
-// that the number of columns a CTA takes (a multiple of ML_MCOLS, or all of them) can follow
-// the size of the launch.
+// The running maximum has a copy per ML_MCOLS columns in the state (see the scan).
 constexpr int ML_MCOLS = 8;
-__host__ __device__ inline int mlstm_lanes(int d) {
-    int l = 1;
-    while (l * ML_ROWS < d) l *= 2;
-    return l;
-}
 __host__ __device__ inline int mlstm_m_copies(int dv) { return (dv + ML_MCOLS - 1) / ML_MCOLS; }
 
 __device__ __forceinline__ void cp_async4(float* dst, const float* src) {
@@ -76,46 +70,52 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-// grid (column blocks, heads, sequences).  Thread groups of L lanes: group g < cols holds
-// column blockIdx.x * cols + g of S, group `cols` holds n (a column whose value is 1; live in
-// the first column block only).  A lane's 16 rows are four quads, quad i = rows
-// (i * L + lane) * 4 .. + 3, so that a group's lanes read consecutive 16-byte pieces of k and
-// q in shared memory and all groups the same pieces.  Tokens come 16 at a time through two
-// buffers filled by asynchronous copies while the lanes work on the other; the first warp
-// turns the chunk's gate logarithms into the factors a_t = exp(f + m_(t-1) - m_t) and
-// b_t = exp(i - m_t) with a scan over the chunk (m -> max(f + m, i) composes: (f2, i2) after
-// (f1, i1) is (f1 + f2, max(f2 + i1, i2))).  The kernel leaves the read-out's numerator
-// S_t^T q_t in `num` and n_t . q_t, exp(-m_t) in `den`; the division is the next kernel's.
-// Every group of eight columns has a copy of the head's running maximum in the state; a CTA
-// reads its first group's and writes all of its groups', so that no CTA reads what another
-// writes.
-template <int L>
-__global__ void __launch_bounds__(288)
+// grid (column blocks of 32, heads, sequences); RW + 1 warps, RW * 16 >= d.  Thread (w, lane)
+// of the first RW warps holds rows w * 16 .. + 15 of column blockIdx.x * 32 + lane of S in
+// registers: all lanes of a warp read the same k and q of a token (one broadcast piece of
+// shared memory at a time) and their own v; a token is one update of the thread's 16 values
+// and its part of the column's dot product with q, which goes to shared memory; the parts
+// of the RW warps are added, for all tokens of a chunk at once, after the chunk.  No shuffle
+// and no other thread's result lies on a token's path.  The last warp has the rows of n dealt
+// round its lanes (n . q by warp sums, a chunk's tokens side by side; written by the first
+// column block only) and, while the
+// others work on a chunk, turns the next chunk's gate logarithms into the factors
+// a_t = exp(f + m_(t-1) - m_t) and b_t = exp(i - m_t) by a scan over the chunk (m -> max(f + m,
+// i) composes: (f2, i2) after (f1, i1) is (f1 + f2, max(f2 + i1, i2))).  Tokens come 16 at a
+// time through two buffers filled by asynchronous copies.  The kernel leaves the read-out's
+// numerator S_t^T q_t in `num` and n_t . q_t, exp(-m_t) in `den`; the division is the next
+// kernel's.  Every group of eight columns has a copy of the head's running maximum in the
+// state; a CTA reads its first group's and writes all of its groups', so that no CTA reads
+// what another writes.
+template <int RW>
+__global__ void __launch_bounds__((RW + 1) * 32)
 mlstm_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ gates,
                   float* __restrict__ num, float* __restrict__ den, int H, int d, int dv,
                   float* __restrict__ state, long long state_stride,
-                  const int* __restrict__ slots, const int* __restrict__ cu_seqlens, int cols) {
+                  const int* __restrict__ slots, const int* __restrict__ cu_seqlens) {
     pdl_wait();
     pdl_launch_next();
     extern __shared__ __align__(16) float sm[];
-    constexpr int DP = L * ML_ROWS;                   // rows, padded
+    constexpr int DP = RW * ML_ROWS;                  // rows, padded
+    constexpr int NR = RW >= 2 ? RW / 2 : 1;          // rows of n a lane of the last warp holds
     constexpr int CH = ML_CHUNK;
-    const int CW = cols;                              // values staged per token
-    const int buf_len = CH * (2 * DP + CW);
-    float* coef = sm + 2 * buf_len;                   // [2][CH][2]: a, b
+    constexpr int CW = ML_COLS;
+    constexpr int BUF = CH * (2 * DP + CW);
+    float* coef = sm + 2 * BUF;                       // [2][CH][2]: a, b
+    float* psum = coef + 4 * CH;                      // [2][CH][RW][CW]
     const int b = blockIdx.z, h = blockIdx.y;
     const int t0 = cu_seqlens[b], t1 = cu_seqlens[b + 1];
     const int slot = slots[b];
-    const int grp = threadIdx.x / L, lane = threadIdx.x % L;
-    const bool is_n = grp == cols;
-    const int col = blockIdx.x * cols + grp;
-    const bool live = is_n ? blockIdx.x == 0 : (grp < cols && col < dv);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool is_nw = warp == RW;
+    const int col = blockIdx.x * CW + lane;
+    const bool live = col < dv;
     const int nq = H * d, C = 2 * nq + H * dv;
     if (slot < 0) {
         // a padding entry: its rows are written, with zeros
         for (int t = t0; t < t1; ++t) {
-            if (live && lane == 0 && !is_n) num[(size_t)t * H * dv + (size_t)h * dv + col] = 0.f;
-            if (live && lane == 0 && is_n) {
+            if (warp == 0 && live) num[(size_t)t * H * dv + (size_t)h * dv + col] = 0.f;
+            if (is_nw && lane == 0 && blockIdx.x == 0) {
                 den[((size_t)t * H + h) * 2] = 0.f;
                 den[((size_t)t * H + h) * 2 + 1] = 1.f;
             }
@@ -125,152 +125,185 @@ mlstm_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ gates
     float* st = state + (size_t)slot * state_stride;
     float* S_g = st + (size_t)h * d * dv;
     float* n_g = st + (size_t)H * d * dv + (size_t)h * d;
-    const int m_copies = mlstm_m_copies(dv);
-    float* m_g = st + (size_t)H * d * dv + (size_t)H * d + (size_t)h * m_copies +
-                 (blockIdx.x * cols) / ML_MCOLS;
+    float* m_g = st + (size_t)H * d * dv + (size_t)H * d + (size_t)h * mlstm_m_copies(dv) +
+                 (blockIdx.x * CW) / ML_MCOLS;
+    // a row warp's thread: S[j] = row warp * 16 + j of its column; the last warp's: its rows
+    // j * 32 + lane of n in S[0 .. NR)
     float S[ML_ROWS];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            const int r = (i * L + lane) * 4 + c;
-            S[i * 4 + c] = !live || r >= d ? 0.f : is_n ? n_g[r] : S_g[(size_t)r * dv + col];
+    for (int j = 0; j < ML_ROWS; ++j) {
+        S[j] = 0.f;
+        if (!is_nw) {
+            const int r = warp * ML_ROWS + j;
+            if (live && r < d) S[j] = S_g[(size_t)r * dv + col];
+        } else if (j < NR) {
+            const int r = j * 32 + lane;
+            if (r < d) S[j] = n_g[r];
         }
+    }
     // the padding rows of both buffers stay zero
-    for (int i = threadIdx.x; i < 2 * buf_len; i += blockDim.x) sm[i] = 0.f;
+    for (int i = threadIdx.x; i < 2 * BUF; i += blockDim.x) sm[i] = 0.f;
     __syncthreads();
-    float m_in = *m_g;                                // (used by the first warp)
+    float m_in = *m_g;                                // (the last warp's)
     const int n_chunks = (t1 - t0 + CH - 1) / CH;
     auto issue = [&](int c) {
-        float* qs = sm + (c & 1) * buf_len;
+        float* qs = sm + (c & 1) * BUF;
         float* ks = qs + CH * DP;
         float* vs = ks + CH * DP;
         const int c0 = t0 + c * CH, nt = min(CH, t1 - c0);
         // a warp a token, lanes along the row: no division in the walk
-        const int warp = threadIdx.x >> 5, ln = threadIdx.x & 31, n_warps = blockDim.x >> 5;
-        for (int tt = warp; tt < nt; tt += n_warps) {
+        for (int tt = warp; tt < nt; tt += RW + 1) {
             const float* row = qkv + (size_t)(c0 + tt) * C + (size_t)h * d;
-            for (int r = ln; r < d; r += 32) {
+            for (int r = lane; r < d; r += 32) {
                 cp_async4(qs + tt * DP + r, row + r);
                 cp_async4(ks + tt * DP + r, row + nq + r);
             }
-            const float* vrow = qkv + (size_t)(c0 + tt) * C + 2 * nq + (size_t)h * dv +
-                                (size_t)blockIdx.x * cols;
-            const int nv = min(CW, dv - (int)blockIdx.x * cols);
-            for (int g = ln; g < nv; g += 32) cp_async4(vs + tt * CW + g, vrow + g);
+            if (live)
+                cp_async4(vs + tt * CW + lane,
+                          qkv + (size_t)(c0 + tt) * C + 2 * nq + (size_t)h * dv + col);
         }
         cp_async_commit();
     };
-    // the first warp's lanes hold the gate logarithms of the chunk they turn into factors next
+    // the last warp's lanes hold the gate logarithms of the chunk they turn into factors next
     float gi = -INFINITY, gf = 0.f;
     auto load_gates = [&](int c) {
         const int c0 = t0 + c * CH, nt = min(CH, t1 - c0);
         gi = -INFINITY, gf = 0.f;                     // (beyond the chunk: m stays)
-        if (threadIdx.x < nt) {
-            gi = gates[(size_t)(c0 + threadIdx.x) * 2 * H + h];
-            gf = gates[(size_t)(c0 + threadIdx.x) * 2 * H + H + h];
+        if (lane < nt) {
+            gi = gates[(size_t)(c0 + lane) * 2 * H + h];
+            gf = gates[(size_t)(c0 + lane) * 2 * H + H + h];
         }
+    };
+    // Scan of a chunk's gates (the last warp): lane t ends with the map of tokens 0..t
+    // composed.  The sums are 64-bit and every m_t is rounded to 32 bits once, so that the
+    // exponents f + m_(t-1) - m_t carry the roundings of the m's they are formed from (a
+    // forget gate next to one moves m by less than its last bit a token).
+    auto factors = [&](int c) {
+        const int c0 = t0 + c * CH, nt = min(CH, t1 - c0);
+        float* cf = coef + (c & 1) * CH * 2;
+        double F = gf, I = gi;
+#pragma unroll
+        for (int o = 1; o < CH; o <<= 1) {
+            const double Fp = __shfl_up_sync(0xffffffffu, F, o);
+            const double Ip = __shfl_up_sync(0xffffffffu, I, o);
+            if (lane >= o) {
+                I = fmax(F + Ip, I);
+                F += Fp;
+            }
+        }
+        const float m_t = (float)fmax(F + (double)m_in, I);
+        float m_p = __shfl_up_sync(0xffffffffu, m_t, 1);
+        if (lane == 0) m_p = m_in;
+        if (lane < nt) {
+            cf[lane * 2] = expf((float)((double)gf + (double)m_p - (double)m_t));
+            cf[lane * 2 + 1] = expf((float)((double)gi - (double)m_t));
+            if (blockIdx.x == 0) den[((size_t)(c0 + lane) * H + h) * 2 + 1] = expf(-m_t);
+        }
+        m_in = __shfl_sync(0xffffffffu, m_t, nt - 1);
     };
     if (n_chunks > 0) {
         issue(0);
-        if (threadIdx.x < 32) load_gates(0);
+        if (is_nw) {
+            load_gates(0);
+            factors(0);
+        }
     }
     for (int c = 0; c < n_chunks; ++c) {
         const int c0 = t0 + c * CH, nt = min(CH, t1 - c0);
-        float* cf = coef + (c & 1) * CH * 2;
-        if (threadIdx.x < 32) {
-            // scan of the chunk's gates: lane t ends with the map of tokens 0..t composed.  The
-            // sums are 64-bit and every m_t is rounded to 32 bits once, so that the exponents
-            // f + m_(t-1) - m_t carry the roundings of the m's they are formed from (a forget
-            // gate next to one moves m by less than its last bit a token)
-            double F = gf, I = gi;
-#pragma unroll
-            for (int o = 1; o < CH; o <<= 1) {
-                const double Fp = __shfl_up_sync(0xffffffffu, F, o);
-                const double Ip = __shfl_up_sync(0xffffffffu, I, o);
-                if ((int)threadIdx.x >= o) {
-                    I = fmax(F + Ip, I);
-                    F += Fp;
-                }
-            }
-            const float m_t = (float)fmax(F + (double)m_in, I);
-            float m_p = __shfl_up_sync(0xffffffffu, m_t, 1);
-            if (threadIdx.x == 0) m_p = m_in;
-            if (threadIdx.x < nt) {
-                cf[threadIdx.x * 2] = expf((float)((double)gf + (double)m_p - (double)m_t));
-                cf[threadIdx.x * 2 + 1] = expf((float)((double)gi - (double)m_t));
-                if (blockIdx.x == 0) den[((size_t)(c0 + threadIdx.x) * H + h) * 2 + 1] = expf(-m_t);
-            }
-            m_in = __shfl_sync(0xffffffffu, m_t, nt - 1);
-        }
+        const float* cf = coef + (c & 1) * CH * 2;
+        float* ps = psum + (c & 1) * CH * RW * CW;
         if (c + 1 < n_chunks) {
             issue(c + 1);
-            if (threadIdx.x < 32) load_gates(c + 1);
+            if (is_nw) load_gates(c + 1);
             cp_async_wait<1>();                       // chunk c has landed, c + 1 is under way
         } else {
             cp_async_wait<0>();
         }
-        __syncthreads();
-        const float* qs = sm + (c & 1) * buf_len;
+        __syncthreads();                              // chunk c and its factors are there
+        const float* qs = sm + (c & 1) * BUF;
         const float* ks = qs + CH * DP;
         const float* vs = ks + CH * DP;
-        // a token's sum over its lanes and its store run under the next token's loads
-        float pend = 0.f;
-        auto finish = [&](int tt, float ds) {
-#pragma unroll
-            for (int o = L >> 1; o > 0; o >>= 1) ds += __shfl_xor_sync(0xffffffffu, ds, o);
-            if (live && lane == 0) {
-                if (is_n) den[((size_t)(c0 + tt) * H + h) * 2] = ds;
-                else num[(size_t)(c0 + tt) * H * dv + (size_t)h * dv + col] = ds;
-            }
-        };
-        const int vcol = min(grp, CW - 1);
+        if (!is_nw) {
+            const float4* kbase = reinterpret_cast<const float4*>(ks + warp * ML_ROWS);
+            const float4* qbase = reinterpret_cast<const float4*>(qs + warp * ML_ROWS);
 #pragma unroll 2
-        for (int tt = 0; tt < nt; ++tt) {
-            const float a = cf[tt * 2], w = cf[tt * 2 + 1];
-            const float vj = vs[tt * CW + vcol];
-            const float4* k4 = reinterpret_cast<const float4*>(ks + tt * DP) + lane;
-            const float4* q4 = reinterpret_cast<const float4*>(qs + tt * DP) + lane;
-            float4 kk[4], qq[4];
+            for (int tt = 0; tt < nt; ++tt) {
+                const float a = cf[tt * 2];
+                const float wv = cf[tt * 2 + 1] * vs[tt * CW + lane];
+                const float4* k4 = kbase + tt * (DP / 4);
+                const float4* q4 = qbase + tt * (DP / 4);
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                kk[i] = k4[i * L];
-                qq[i] = q4[i * L];
+                for (int j = 0; j < ML_ROWS / 4; ++j) {
+                    const float4 kk = k4[j], qq = q4[j];
+                    S[j * 4 + 0] = fmaf(wv, kk.x, a * S[j * 4 + 0]);
+                    S[j * 4 + 1] = fmaf(wv, kk.y, a * S[j * 4 + 1]);
+                    S[j * 4 + 2] = fmaf(wv, kk.z, a * S[j * 4 + 2]);
+                    S[j * 4 + 3] = fmaf(wv, kk.w, a * S[j * 4 + 3]);
+                    acc[0] = fmaf(S[j * 4 + 0], qq.x, acc[0]);
+                    acc[1] = fmaf(S[j * 4 + 1], qq.y, acc[1]);
+                    acc[2] = fmaf(S[j * 4 + 2], qq.z, acc[2]);
+                    acc[3] = fmaf(S[j * 4 + 3], qq.w, acc[3]);
+                }
+                ps[(tt * RW + warp) * CW + lane] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
             }
-            if (tt > 0) finish(tt - 1, pend);
-            const float wv = is_n ? w : w * vj;
-            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        } else {
+            // n over the chunk, each lane's part of every token's n . q kept; then the warp
+            // sums of all the chunk's tokens side by side (their shuffles overlap)
+            float dn[CH];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                S[i * 4 + 0] = fmaf(wv, kk[i].x, a * S[i * 4 + 0]);
-                S[i * 4 + 1] = fmaf(wv, kk[i].y, a * S[i * 4 + 1]);
-                S[i * 4 + 2] = fmaf(wv, kk[i].z, a * S[i * 4 + 2]);
-                S[i * 4 + 3] = fmaf(wv, kk[i].w, a * S[i * 4 + 3]);
-                acc[0] = fmaf(S[i * 4 + 0], qq[i].x, acc[0]);
-                acc[1] = fmaf(S[i * 4 + 1], qq[i].y, acc[1]);
-                acc[2] = fmaf(S[i * 4 + 2], qq[i].z, acc[2]);
-                acc[3] = fmaf(S[i * 4 + 3], qq[i].w, acc[3]);
-            }
-            pend = (acc[0] + acc[1]) + (acc[2] + acc[3]);
-        }
-        if (nt > 0) finish(nt - 1, pend);
-        __syncthreads();                              // everybody is done with this buffer
-    }
-    if (t1 > t0 && live) {
+            for (int tt = 0; tt < CH; ++tt) {
+                dn[tt] = 0.f;
+                if (tt < nt) {
+                    const float a = cf[tt * 2], w = cf[tt * 2 + 1];
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const int r = (i * L + lane) * 4 + c;
-                if (r < d) {
-                    if (is_n) n_g[r] = S[i * 4 + c];
-                    else S_g[(size_t)r * dv + col] = S[i * 4 + c];
+                    for (int j = 0; j < NR; ++j) {
+                        const int r = j * 32 + lane;
+                        const float kk = r < DP ? ks[tt * DP + r] : 0.f;
+                        const float qq = r < DP ? qs[tt * DP + r] : 0.f;
+                        S[j] = fmaf(w, kk, a * S[j]);
+                        dn[tt] = fmaf(S[j], qq, dn[tt]);
+                    }
                 }
             }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+                for (int tt = 0; tt < CH; ++tt) dn[tt] += __shfl_xor_sync(0xffffffffu, dn[tt], o);
+            if (blockIdx.x == 0) {
+                float mine = 0.f;
+#pragma unroll
+                for (int tt = 0; tt < CH; ++tt)
+                    if (lane == tt) mine = dn[tt];
+                if (lane < nt) den[((size_t)(c0 + lane) * H + h) * 2] = mine;
+            }
+            if (c + 1 < n_chunks) factors(c + 1);
+        }
+        __syncthreads();                              // the chunk's parts are there
+        for (int idx = threadIdx.x; idx < nt * CW; idx += blockDim.x) {
+            const int tt = idx / CW, l = idx % CW;
+            float sum = 0.f;
+#pragma unroll
+            for (int w = 0; w < RW; ++w) sum += ps[(tt * RW + w) * CW + l];
+            if (blockIdx.x * CW + l < dv)
+                num[(size_t)(c0 + tt) * H * dv + (size_t)h * dv + blockIdx.x * CW + l] = sum;
+        }
     }
-    if (t1 > t0 && threadIdx.x == 0) {
-        const int mine = min(cols, dv - (int)blockIdx.x * cols);
-        for (int i = 0; i * ML_MCOLS < mine; ++i) m_g[i] = m_in;
+    if (t1 > t0) {
+#pragma unroll
+        for (int j = 0; j < ML_ROWS; ++j) {
+            if (!is_nw) {
+                const int r = warp * ML_ROWS + j;
+                if (live && r < d) S_g[(size_t)r * dv + col] = S[j];
+            } else if (j < NR && blockIdx.x == 0) {
+                const int r = j * 32 + lane;
+                if (r < d) n_g[r] = S[j];
+            }
+        }
+        if (is_nw && lane == 0) {
+            const int mine = min(CW, dv - (int)blockIdx.x * CW);
+            for (int i = 0; i * ML_MCOLS < mine; ++i) m_g[i] = m_in;
+        }
     }
 }
 
@@ -340,41 +373,25 @@ AGV_API int agv_mlstm_scan(const float* qkv, const float* gates, float* num, flo
                            int B, int H, int d, int dv, float* state, long long state_stride,
                            const int* slots, const int* cu_seqlens, cudaStream_t stream) {
     AGV_REQUIRE(T >= 0 && B > 0 && H > 0 && d > 0 && dv > 0, "mlstm_scan: bad sizes");
-    AGV_REQUIRE(d <= 16 * ML_ROWS, "mlstm_scan: head size %d exceeds %d", d, 16 * ML_ROWS);
+    AGV_REQUIRE(d <= 256, "mlstm_scan: head size %d exceeds 256", d);
     AGV_REQUIRE(state_stride >= agv_mlstm_state_numel(H, d, dv), "mlstm_scan: state too small");
     AGV_REQUIRE(agv_aligned(den, 8), "mlstm_scan: den must be 8-byte aligned");
     if (T == 0) return 0;
-    const int L = mlstm_lanes(d);
-    // columns a CTA: as many as 256 threads hold, fewer (down to eight) while that still
-    // leaves every CTA an SM of its own.  (Measured on one prompt of 2,048 tokens, 32 heads of
-    // 128 x 128: 128 CTAs of 32 columns 851 us; 256 of 16, two to an SM, 941; 512 of 8, 1,027:
-    // a token costs a warp about 800 cycles whatever its company.)
-    int cols = 256 / L;
-    if (cols > dv) cols = dv;
-    static int sms = 0;
-    if (!sms) {
-        int dev = 0;
-        AGV_CUDA_OK(cudaGetDevice(&dev));
-        AGV_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    }
-    while (cols % (2 * ML_MCOLS) == 0 && (long long)H * B * ((dv + cols - 1) / cols) * 2 <= sms)
-        cols /= 2;
-    const int blocks = (dv + cols - 1) / cols;
-    // (a warp holds whole groups: (cols + 1) * L is rounded up to a warp by idle threads)
-    const int threads = ((cols + 1) * L + 31) / 32 * 32;
-    const dim3 grid((unsigned)blocks, (unsigned)H, (unsigned)B);
-    const size_t smem = ((size_t)2 * ML_CHUNK * (2 * L * ML_ROWS + cols) + 4 * ML_CHUNK) *
-                        sizeof(float);
-#define AGV_SCAN(LL)                                                                          \
+    int RW = 1;
+    while (RW * ML_ROWS < d) RW *= 2;
+    const dim3 grid((unsigned)((dv + ML_COLS - 1) / ML_COLS), (unsigned)H, (unsigned)B);
+    const size_t smem = ((size_t)2 * ML_CHUNK * (2 * RW * ML_ROWS + ML_COLS) + 4 * ML_CHUNK +
+                         (size_t)2 * ML_CHUNK * RW * ML_COLS) * sizeof(float);
+#define AGV_SCAN(RR)                                                                          \
     do {                                                                                      \
-        auto kern = mlstm_scan_kernel<LL>;                                                    \
+        auto kern = mlstm_scan_kernel<RR>;                                                    \
         if (smem > 48 * 1024)                                                                 \
             AGV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                              (int)smem));                                     \
-        agv_launch_after(kern, grid, threads, smem, stream, qkv, gates, num, den, H, d, dv,   \
-                         state, state_stride, slots, cu_seqlens, cols);                       \
+        agv_launch_after(kern, grid, (RR + 1) * 32, smem, stream, qkv, gates, num, den, H, d, \
+                         dv, state, state_stride, slots, cu_seqlens);                         \
     } while (0)
-    switch (L) {
+    switch (RW) {
         case 1: AGV_SCAN(1); break;
         case 2: AGV_SCAN(2); break;
         case 4: AGV_SCAN(4); break;
