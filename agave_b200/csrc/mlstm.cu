@@ -385,9 +385,12 @@ AGV_API int agv_mlstm_scan(const float* qkv, const float* gates, float* num, flo
 #define AGV_SCAN(RR)                                                                          \
     do {                                                                                      \
         auto kern = mlstm_scan_kernel<RR>;                                                    \
-        if (smem > 48 * 1024)                                                                 \
+        static bool configured = false;          /* (the size follows from RR alone) */       \
+        if (smem > 48 * 1024 && !configured) {                                                \
             AGV_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                              (int)smem));                                     \
+            configured = true;                                                                \
+        }                                                                                     \
         agv_launch_after(kern, grid, (RR + 1) * 32, smem, stream, qkv, gates, num, den, H, d, \
                          dv, state, state_stride, slots, cu_seqlens);                         \
     } while (0)
