@@ -666,6 +666,41 @@ def chosen_by(eng, toks):
     return {i: rec[id(b.ffn)] for i, b in enumerate(eng.model.blocks) if id(b.ffn) in rec}
 
 
+class RecordedRoutes:
+    """While active, every routed feed-forward's choice is kept, step by step: ``steps[k][i]`` is
+    the ids [tokens of step k, top] of layer i.  ``of_rows`` puts a request's rows together
+    again from (step, first row, rows) pieces, as the plain model's ``chosen`` wants them."""
+
+    def __init__(self, eng):
+        self.eng, self.steps, self._cur = eng, [], None
+
+    def __enter__(self):
+        from agave_b200.parts.moe import RoutedFeedForward
+        self._cls, self._keep = RoutedFeedForward, RoutedFeedForward.route
+        layer_of = {id(b.ffn): i for i, b in enumerate(self.eng.model.blocks)}
+        rec = self
+
+        def route(part, x):
+            ids, wts = rec._keep(part, x)
+            rec._cur[layer_of[id(part)]] = ids.cpu().long()
+            return ids, wts
+        RoutedFeedForward.route = route
+        return self
+
+    def __exit__(self, *exc):
+        self._cls.route = self._keep
+
+    def step(self, entries, want):
+        self._cur = {}
+        out = self.eng.step(entries, want)
+        self.steps.append(self._cur)
+        return out
+
+    def of_rows(self, pieces):
+        layers = self.steps[pieces[0][0]].keys()
+        return {i: torch.cat([self.steps[k][i][a:a + n] for k, a, n in pieces]) for i in layers}
+
+
 def reference(eng, folder, toks, dtype):
     """The plain model's logits; in bfloat16 under the experts the library chose, since a
     close call that falls the other way moves a row far more than rounding does."""

@@ -15,7 +15,7 @@ import torch
 
 from kadavik_util import (attention, config, dense, mlstm, moe, plain_logits, rotation, tokens,
                           write_folder)
-from test_kadavik_gpu import TD, alone, reference, rows_agree
+from test_kadavik_gpu import TD, RecordedRoutes, reference, rows_agree
 
 pytestmark = pytest.mark.gpu
 
@@ -82,7 +82,9 @@ def draw(seed):
     return config(width, vocab, layers, eps=rng.choice([1e-6, 1e-5, 1e-3]),
                   embed_scale=rng.choice([None, 4.0, 11.5]),
                   logit_scale=rng.choice([None, 0.25, 3.0]),
-                  side=rng.choice([None, 1, 6, 16]))
+                  # (a token input one wide is a sign: y / rms(y) jumps where its gate crosses zero,
+                  # and no comparison holds there)
+                  side=rng.choice([None, 2, 6, 16]))
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -94,33 +96,50 @@ def test_a_drawn_configuration(seed, dtype):
     try:
         eng = Engine(folder, dtype=dtype, max_tokens=4096)
         V = cfg["vocab"]
+        # (bfloat16: the plain model runs under the experts the library chose in the very
+        # steps that are compared; a close call may fall differently from step to step)
+        def plain(toks, rec, pieces):
+            if dtype == "float32":
+                return plain_logits(folder, toks)
+            return plain_logits(folder, toks, chosen=rec.of_rows(pieces))
         # a cut request: most of it at once, the rest token by token
         toks = tokens(150 + 7 * seed, V, seed)
-        rows_agree(alone(eng, toks, len(toks) - 20), reference(eng, folder, toks, dtype), dtype,
-                   f"seed {seed} alone")
+        cut = len(toks) - 20
+        with RecordedRoutes(eng) as rec:
+            s0 = eng.acquire()
+            got = [rec.step([(s0, toks[:cut])], [list(range(cut))])]
+            for p in range(cut, len(toks)):
+                got.append(rec.step([(s0, [toks[p]])], [[0]]))
+            eng.release(s0)
+        pieces = [(0, 0, cut)] + [(k, 0, 1) for k in range(1, len(toks) - cut + 1)]
+        rows_agree(torch.cat(got), plain(toks, rec, pieces), dtype, f"seed {seed} alone")
         # an unequal batch decoded together; the shorter request ends first
         seqs = [tokens(n, V, 100 + seed + n) for n in (70 + seed, 9, 1 + seed)]
         lens = [len(s) - 4 - 2 * i for i, s in enumerate(seqs)]
         lens = [max(1, n) for n in lens]
         slots = [eng.acquire() for _ in seqs]
         got = [[] for _ in seqs]
-        out = eng.step([(sl, s[:n]) for sl, s, n in zip(slots, seqs, lens)],
-                       [list(range(n)) for n in lens])
-        o = 0
-        for i, n in enumerate(lens):
-            got[i].append(out[o:o + n])
-            o += n
-        at = list(lens)
-        while any(a < len(s) for a, s in zip(at, seqs)):
-            live = [i for i in range(len(seqs)) if at[i] < len(seqs[i])]
-            out = eng.step([(slots[i], [seqs[i][at[i]]]) for i in live], [[0]] * len(live))
-            for r, i in enumerate(live):
-                got[i].append(out[r:r + 1])
-                at[i] += 1
+        pieces = [[] for _ in seqs]
+        with RecordedRoutes(eng) as rec:
+            out = rec.step([(sl, s[:n]) for sl, s, n in zip(slots, seqs, lens)],
+                           [list(range(n)) for n in lens])
+            o = 0
+            for i, n in enumerate(lens):
+                got[i].append(out[o:o + n])
+                pieces[i].append((0, o, n))
+                o += n
+            at = list(lens)
+            while any(a < len(s) for a, s in zip(at, seqs)):
+                live = [i for i in range(len(seqs)) if at[i] < len(seqs[i])]
+                out = rec.step([(slots[i], [seqs[i][at[i]]]) for i in live], [[0]] * len(live))
+                for r, i in enumerate(live):
+                    got[i].append(out[r:r + 1])
+                    pieces[i].append((len(rec.steps) - 1, r, 1))
+                    at[i] += 1
         for sl in slots:
             eng.release(sl)
         for i, s in enumerate(seqs):
-            rows_agree(torch.cat(got[i]), reference(eng, folder, s, dtype), dtype,
+            rows_agree(torch.cat(got[i]), plain(s, rec, pieces[i]), dtype,
                        f"seed {seed} request {i}")
         # greedy generation through the scheduler
         prompts = [tokens(n, V, 500 + seed + n) for n in (3, 40)]
