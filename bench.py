@@ -327,18 +327,18 @@ def compare_configs_kadavik(size):
     """Kadavik beside Bovozen, the library's other decoder with a recurrent mixer, routed
     experts and a shared one: equal width, heads, head size, experts, layers and vocabulary.
     Kadavik's layers alternate attention (four taps on q, k and v, half the head rotated, a
-    window of 1,024 behind which four keys stay, an output gate) with the matrix memory (as
+    window of 1,024 behind which eight keys stay, an output gate) with the matrix memory (as
     many heads, state head size x head size per head); its routers have two identity outputs
     beyond the experts; every layer takes a token input 64 wide."""
     H, A, G, d, E, top, ff, groups, keep, L, V = COMPARE_SIZES[size]
     att = {"conv": 4, "dim": d, "heads": A, "kv_heads": G,
-           "mask": {"keep_first": 4, "size": 1024},
-           "rot": {"base": 500000.0, "dims": d // 2,
+           "mask": {"keep_first": 8, "size": 1024},
+           "rot": {"base": 1000000.0, "dims": d // 2,
                    "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}},
            "scale": d ** -0.5, "vdim": d}
     rec = {"dim": d, "gate_cap": 15.0, "heads": A, "vdim": d}
     mlp = {"expert": {"ff": ff}, "kind": "moe",
-           "router": {"experts": E, "identity": 2, "scale": 2.0, "top": top},
+           "router": {"experts": E, "identity": 2, "scale": 1.5, "top": top},
            "shared": {"ff": 2 * ff}}
     layers = [{"mixer": rec if l % 2 else att, "mlp": mlp,
                "type": "mlstm" if l % 2 else "attention"} for l in range(L)]

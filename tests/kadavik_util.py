@@ -89,7 +89,7 @@ K1 = config(72, 210, [
 # K2: the sizes that take the tensor-core kernels (head sizes 64, four query heads per kv
 # head, windows that cross pages), a window without kept keys (a ring in the cache), four taps.
 K2 = config(128, 320, [
-    (mlstm(4, 64, 64, 15.0), moe(8, 2, 3, 64, scale=2.5, shared=128)),
+    (mlstm(4, 64, 64, 12.0), moe(7, 2, 3, 64, scale=2.5, shared=96)),
     (attention(4, 1, 64, 64, 0.13, conv=4, size=100, keep_first=3,
                rot=rotation(32, 500.0, (4.0, 2.0, 8.0, 64))), moe(8, 1, 2, 64, scale=1.0)),
     (mlstm(2, 32, 128, 10.0), dense(192)),

@@ -191,7 +191,7 @@ def _moe_part(W, H, E, I, top, ff, shared, scale, td):
 
 
 MOE = [(1, 72, 5, 1, 2, 24, 0, 1.5), (40, 96, 1, 0, 1, 32, 0, 1.0), (33, 128, 4, 0, 4, 64, 8, 1.0),
-       (200, 128, 8, 2, 3, 64, 128, 2.5), (130, 80, 3, 3, 2, 16, 20, 0.7), (9, 64, 2, 4, 6, 24, 0, 2.0)]
+       (200, 128, 7, 2, 3, 64, 96, 2.5), (130, 80, 3, 3, 2, 16, 20, 0.7), (9, 64, 2, 4, 6, 24, 0, 2.0)]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -267,7 +267,7 @@ def _mlstm_part(W, A, d, dv, H, cap, td, eps=1e-5):
     return part
 
 
-MLSTM = [(3, 12, 10, 72, 8.0), (4, 64, 64, 128, 15.0), (1, 16, 48, 96, 1.0), (2, 20, 6, 80, 15.0),
+MLSTM = [(3, 12, 10, 72, 8.0), (4, 64, 64, 128, 12.0), (1, 16, 48, 96, 1.0), (2, 20, 6, 80, 15.0),
          (2, 128, 128, 64, 5.0), (1, 200, 24, 40, 3.0), (5, 8, 8, 48, 30.0)]
 
 
@@ -502,7 +502,7 @@ def _mark_weights(W, m, td, strength=1.6):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("size, keep, taps, d, dv", [(72, 4, 4, 64, 64), (20, 3, 2, 24, 16),
+@pytest.mark.parametrize("size, keep, taps, d, dv", [(76, 6, 4, 64, 64), (20, 3, 2, 24, 16),
                                                       (64, 1, 3, 32, 32), (130, 7, None, 16, 16),
                                                       (100, 70, 2, 128, 128), (90, 5, 3, 64, 32)])
 def test_the_key_at_a_window_edge_or_a_kept_place_decides(dtype, size, keep, taps, d, dv):
@@ -528,7 +528,7 @@ def test_the_key_at_a_window_edge_or_a_kept_place_decides(dtype, size, keep, tap
             assert rel_err(_run_alone(part, h, new, td), ref) < tol, (mark, new[:2])
 
 
-@pytest.mark.parametrize("hd, window, keep, T", [(64, 72, 4, 300), (128, 100, 70, 260),
+@pytest.mark.parametrize("hd, window, keep, T", [(64, 76, 6, 300), (128, 100, 70, 260),
                                                  (32, 64, 1, 200), (64, 130, 65, 400)])
 def test_kept_keys_in_every_form_of_the_prompt_kernels(hd, window, keep, T):
     """bfloat16: the one-warp, the mma.sync and the tcgen05 prompt kernels on the same q, k, v
