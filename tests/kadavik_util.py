@@ -126,7 +126,18 @@ K4 = config(76, 211, [
     (attention(2, 1, 20, 12, 0.35, size=200, rot=rotation(10, 2000.0), kv_from=2), dense(44)),
 ], eps=2e-5, embed_scale=5.0, logit_scale=1.7, side=3)
 
-CONFIGS = {"K1": K1, "K2": K2, "K3": K3, "K4": K4}
+# K5: windows without kept keys, so that the cache keeps rings of them, each read by a second
+# layer through the same mask.
+K5 = config(128, 200, [
+    (attention(4, 2, 64, 64, 0.15, conv=3, size=70, keep_first=0, rot=rotation(32, 1e4)), dense(64)),
+    (mlstm(2, 32, 32, 10.0), None),
+    (attention(8, 2, 64, 64, 0.15, conv=2, size=70, keep_first=0, rot=rotation(32, 1e4), kv_from=0),
+     dense(64)),
+    (attention(2, 1, 16, 16, 0.3, size=130), None),
+    (attention(2, 1, 16, 16, 0.3, size=130, kv_from=3), dense(32)),
+], eps=1e-5, embed_scale=2.0, side=4)
+
+CONFIGS = {"K1": K1, "K2": K2, "K3": K3, "K4": K4, "K5": K5}
 
 
 def make_tensors(cfg, seed, dtype):

@@ -976,7 +976,7 @@ def test_command_line_on_this_architecture():
         assert outs[0] == outs[1] and len(outs[0]) == 5
 
 
-@pytest.mark.parametrize("name, room", [("K1", 60), ("K2", 90), ("K3", 64)])
+@pytest.mark.parametrize("name, room", [("K1", 60), ("K2", 90), ("K3", 64), ("K5", 100)])
 def test_a_cache_shorter_than_a_page_or_a_window(name, room):
     """32-bit: a cache of one or two pages.  A window that still fits a sequence keeps its
     edge (and the kept keys behind it); a window no sequence can outgrow is none."""
